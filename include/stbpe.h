@@ -1,0 +1,152 @@
+/*
+ * stbpe -- B200 (sm_100a) BPE merge-loop engine, C ABI.
+ *
+ * One engine handle per GPU / rank.  All entry points return an int status
+ * (STBPE_OK = 0); stbpe_last_error() gives a message for the last failure on a
+ * handle.  No entry point takes or returns a torch type: pointers and sizes only.
+ * Pointers marked "host or device" are classified with cudaPointerGetAttributes.
+ * Calls on one handle come from one host thread at a time (the reference drives
+ * its trainer from a single thread, gpu_tokenizer/bpe_trainer.py:2501).
+ *
+ * The citations name the reference interface each entry point stands in for
+ * (paths relative to the reference project).
+ */
+#ifndef STBPE_H
+#define STBPE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define STBPE_OK 0
+#define STBPE_E_BADARG 1     /* ValueError / TypeError in the reference (cuda_kernels.py:761-775) */
+#define STBPE_E_CAPACITY 2   /* RuntimeError("pair workspace capacity exceeded") (utils.py:619-620) */
+#define STBPE_E_TIMEOUT 3    /* a bounded device-side wait gave up */
+#define STBPE_E_CUDA 4       /* any CUDA runtime failure; OOM text contains "CUDA out of memory" */
+#define STBPE_E_ID_OVERFLOW 5 /* OverflowError: id above the supported range (utils.py:436-439) */
+#define STBPE_E_STATE 6      /* call made in the wrong state (e.g. training before counting) */
+
+/* stop reasons reported by stbpe_get_state */
+#define STBPE_RUNNING 0
+#define STBPE_STOP_TARGET 1     /* requested number of merges reached */
+#define STBPE_STOP_NO_PAIRS 2   /* no adjacent pair left (bpe_trainer.py:4304-4308) */
+#define STBPE_STOP_LOW_COUNT 3  /* best count < 2 (bpe_trainer.py:2491-2494, :4361-4364) */
+#define STBPE_STOP_ERROR 4      /* device error flag set; see stbpe_last_error */
+
+typedef struct stbpe_engine stbpe_engine;
+
+typedef struct stbpe_config {
+    int32_t device;          /* CUDA device ordinal */
+    int32_t base_vocab;      /* first merge gets id base_vocab (bpe_trainer.py:4365) */
+    int64_t max_tokens;      /* capacity of the token stream on this engine */
+    int64_t table_slots;     /* pair table capacity, rounded up to a power of two; 0 = auto */
+    int32_t max_merges;      /* capacity of the merge log */
+    int32_t world_size;      /* >1: pair keys are owned by hash(key) % world_size */
+    int32_t rank;
+    int32_t reserved;
+} stbpe_config;
+
+typedef struct stbpe_state {
+    int32_t merges_done;
+    int32_t stop_reason;      /* STBPE_RUNNING ... */
+    int64_t live_tokens;      /* tokens currently in the stream */
+    int64_t table_keys;       /* distinct keys ever inserted into the pair table */
+    int64_t table_slots;
+    uint32_t device_error;    /* raw device error bits (0 = none) */
+    int32_t n_tiles;
+} stbpe_state;
+
+/* Lifetime.  Replaces GPUBPETrainer's per-fit device contexts and workspaces
+ * (gpu_tokenizer/bpe_trainer.py:2907-2934, :224-282). */
+int stbpe_create(stbpe_engine **out, const stbpe_config *cfg);
+int stbpe_destroy(stbpe_engine *e);
+const char *stbpe_last_error(const stbpe_engine *e);
+const char *stbpe_version(void);
+
+/* Ingest: pack rows into the flat int32 token stream (bit 31 = first token of a row).
+ * Replaces BytePacker.encode_view + the batcher fill + GPUBatchRecord.from_cpu
+ * (gpu_tokenizer/cpu_packer.py:17-61, datasets.py:75-84, bpe_trainer.py:137-222).
+ * Rows are appended after the rows of earlier calls; empty rows own no pair and
+ * vanish.  row_offsets has n_rows+1 entries (host memory), offsets into data.
+ * stbpe_reset drops the stream, the table and the merge log. */
+int stbpe_reset(stbpe_engine *e);
+int stbpe_append_bytes(stbpe_engine *e, const uint8_t *data /* host or device */, int64_t n,
+                       const int64_t *row_offsets, int64_t n_rows, void *stream);
+int stbpe_append_ids(stbpe_engine *e, const int32_t *ids /* host or device */, int64_t n,
+                     const int64_t *row_offsets, int64_t n_rows, void *stream);
+
+/* Full adjacent-pair histogram of the current stream into the pair table.
+ * Replaces utils.count_pairs + aggregate_pair_keys (gpu_tokenizer/utils.py:558-635,
+ * :709-751).  Clears the table first, so it may also be called after merges to
+ * recount from the rewritten stream. */
+int stbpe_count_initial(stbpe_engine *e, void *stream);
+
+/* Best pair: maximum count, ties to the smallest packed key (a<<32)|b.
+ * Replaces select_best_pair (gpu_tokenizer/trainers/bpe_gpu.py:96-130).  count 0 =
+ * empty histogram.  n_ties = number of keys holding the maximum count. */
+int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *count, int64_t *n_ties, void *stream);
+
+/* Apply one merge to every row and update the pair table by the +-deltas only.
+ * Replaces utils.apply_merge_once + compact_tokens_inplace
+ * (gpu_tokenizer/utils.py:413-555, :347-410) followed by the recount of the next
+ * loop iteration.  The merge is appended to the merge log with the count the
+ * table held for (a, b).  n_matches may be NULL. */
+int stbpe_apply_merge(stbpe_engine *e, int32_t a, int32_t b, int32_t new_id, int64_t *n_matches,
+                      void *stream);
+
+/* The merge loop (gpu_tokenizer/bpe_trainer.py:4193-4517) run on the device without
+ * a host round trip per merge: select -> stop rules -> apply, n_merges times or until a
+ * stop rule fires.  Synchronises the stream before returning. */
+int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream);
+
+int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *stream);
+/* merges: 2*n int32 (a, b); counts: n int64 (may be NULL); live_before: n int64, live
+ * tokens before each merge (may be NULL).  Host pointers. */
+int stbpe_get_merges(stbpe_engine *e, int32_t first, int32_t n, int32_t *merges, int64_t *counts,
+                     int64_t *live_before);
+
+/* Export of the pair table as the reference returns histograms: unique keys ascending,
+ * int64 counts, zero-count keys dropped (gpu_tokenizer/utils.py:709-751).  keys/counts
+ * are device pointers with room for cap entries. */
+int stbpe_export_histogram(stbpe_engine *e, uint64_t *keys, int64_t *counts, int64_t cap,
+                           int64_t *n_out, void *stream);
+/* Export of the rewritten stream: ids (device, cap tokens, bit 31 = row start). */
+int stbpe_export_stream(stbpe_engine *e, int32_t *ids, int64_t cap, int64_t *n_out, void *stream);
+
+/* Multi-GPU exchange steps (one engine per rank; the collective itself is issued by
+ * the host between these calls).  Replaces reduce_pair_histograms
+ * (gpu_tokenizer/utils.py:863-978) with an exchange of deltas.
+ *   stbpe_mg_outbox : device buffer [world_size][cap_per_peer] of (key, delta) 16-byte
+ *                     entries preceded by a per-peer int64 count array.
+ *   stbpe_mg_count_local / stbpe_mg_merge_local fill the outbox instead of the table;
+ *   stbpe_mg_apply_inbox adds a received buffer of the same layout into the table slice;
+ *   stbpe_mg_candidate writes this rank's best (key, count) to a device pointer;
+ *   stbpe_mg_commit takes the winning (key, count) chosen identically on every rank. */
+int stbpe_mg_buffers(stbpe_engine *e, void **outbox, void **inbox, int64_t *cap_per_peer,
+                     int64_t *bytes_per_peer);
+int stbpe_mg_count_local(stbpe_engine *e, void *stream);
+int stbpe_mg_merge_local(stbpe_engine *e, void *stream);
+int stbpe_mg_apply_inbox(stbpe_engine *e, void *stream);
+int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev /* 2 x int64: key, count */, void *stream);
+int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev /* world x 2 int64 */, void *stream);
+
+/* Stateless operators on padded [B, L] batches resident on the device, with the
+ * reference's operator signatures.
+ * stbpe_rows_count_pairs  <- utils.count_pairs (gpu_tokenizer/utils.py:691-706): unique
+ *   (a, b) rows ascending into pair_keys[cap][2] (rest -1), int64 counts (rest 0), length.
+ * stbpe_rows_apply_merge  <- utils.apply_merge_once / cuda_kernels.apply_merge_and_compact
+ *   (gpu_tokenizer/utils.py:413-555, cuda_kernels.py:725-832): in place on tokens/valid,
+ *   lengths int32[B], spans uint8 [B][L-1] in pre-compaction coordinates (may be NULL). */
+int stbpe_rows_count_pairs(const int32_t *tokens, const uint8_t *valid, int64_t B, int64_t L,
+                           int32_t *pair_keys, int64_t *pair_counts, int64_t cap,
+                           int64_t *length_dev, void *stream);
+int stbpe_rows_apply_merge(int32_t *tokens, uint8_t *valid, int32_t *lengths, int64_t B, int64_t L,
+                           int32_t a, int32_t b, int32_t new_id, uint8_t *spans, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STBPE_H */

@@ -1,0 +1,291 @@
+// Shared device-side definitions of the BPE merge-loop engine (sm_100a).
+//
+// Data layout in HBM
+//   token stream : tiles of STBPE_TILE uint32 words; a tile keeps its live tokens compacted
+//                  at the front, its length lives in the tile record.  Bit 31 of a word
+//                  marks the first token of a row; a pair (i, i+1) is countable iff token
+//                  i+1 does not carry that bit (rows are the only pair-breaking boundary,
+//                  gpu_tokenizer/utils.py:586).
+//   tile records : two versioned 32-byte records per tile {ver, len, first three live
+//                  tokens, last live token}.  During merge number m a tile is rewritten in
+//                  place by exactly one CTA, while neighbouring CTAs need its PRE-merge
+//                  head and tail.  A writer therefore fills the record with the older
+//                  version and stamps it m; readers use the record with the largest
+//                  version below m, which nobody writes during merge m.
+//   pair table   : open addressing, linear probing, 16-byte slots {key = (a<<32)|b,
+//                  int64 count}.  Keys are never removed; a count may return to zero.
+//   block maxima : best (count, smallest key) of every block of 256 slots; only blocks
+//                  touched by a merge are recomputed, the arg-max reduces the maxima.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define STBPE_TILE 4096
+#define STBPE_NT 512
+#define STBPE_IPT (STBPE_TILE / STBPE_NT)
+#define STBPE_NW (STBPE_NT / 32)
+#define STBPE_NONE 0xFFFFFFFFu
+#define STBPE_FLAG 0x80000000u
+#define STBPE_IDMASK 0x7FFFFFFFu
+#define STBPE_EMPTY 0xFFFFFFFFFFFFFFFFull
+#define STBPE_BLK 256
+#define STBPE_MAX_PROBE (1u << 20)
+
+// device error bits
+#define STBPE_DERR_TABLE_FULL 1u
+#define STBPE_DERR_OUTBOX_FULL 2u
+#define STBPE_DERR_LTABLE_FULL 4u
+#define STBPE_DERR_KEY_MISSING 8u
+#define STBPE_DERR_BAD_ID 16u
+
+typedef unsigned long long u64;
+typedef long long i64;
+
+struct __align__(16) Slot {
+    u64 key;
+    i64 count;
+};
+
+struct __align__(16) TileRec {
+    int ver;  // merge number that wrote this record; 0 = written at load; <0 = never written
+    int len;
+    uint32_t head[3];
+    uint32_t tail;
+    uint32_t pad[2];
+};
+
+struct DevState {
+    int cur_a, cur_b, cur_new, pad0;
+    i64 cur_count;
+    int merges_done, target, base_vocab, stopped;
+    int stop_reason;
+    unsigned int n_dirty;
+    unsigned int error;
+    unsigned int ticket;
+    u64 n_keys;
+    i64 n_live;
+    i64 n_matches;
+    u64 peek_key;
+    i64 peek_count;
+    i64 peek_ties;
+    unsigned int n_ltouched;
+    unsigned int ticket2;
+    i64 export_n;
+};
+
+struct EngineDev {
+    uint32_t *tiles;
+    TileRec *recs;  // 2 per tile
+    int n_tiles;
+    Slot *table;
+    u64 mask;
+    Slot *blockmax;
+    unsigned int *dirty_flag;
+    unsigned int *dirty_list;
+    unsigned int n_blocks;
+    DevState *st;
+    int32_t *merges;
+    i64 *merge_counts;
+    i64 *live_before;
+    // multi-GPU: rank-local delta table, emptied into the per-owner outbox
+    int world, rank;
+    Slot *ltable;
+    u64 lmask;
+    unsigned int *ltouched;
+    Slot *outbox;  // [world][1 + cap] entries; entry 0 of a chunk = {count, 0}
+    Slot *inbox;
+    i64 cap_per_peer;
+};
+
+__device__ __forceinline__ u64 mix64(u64 x) {
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdULL;
+    x ^= x >> 33;
+    x *= 0xc4ceb9fe1a85ec53ULL;
+    x ^= x >> 33;
+    return x;
+}
+
+__device__ __forceinline__ int owner_of(u64 key, int world) {
+    return (int)((mix64(key) >> 40) % (u64)world);
+}
+
+__device__ __forceinline__ bool better(u64 k1, i64 c1, u64 k2, i64 c2) {
+    // (k1, c1) beats (k2, c2): larger count, ties to the smaller packed key
+    // (gpu_tokenizer/trainers/bpe_gpu.py:106-127)
+    return c1 > c2 || (c1 == c2 && k1 < k2);
+}
+
+__device__ __forceinline__ void mark_dirty(const EngineDev &e, u64 slot_index) {
+    unsigned int blk = (unsigned int)(slot_index / STBPE_BLK);
+    if (*(volatile unsigned int *)&e.dirty_flag[blk] == 0u) {
+        if (atomicExch(&e.dirty_flag[blk], 1u) == 0u) {
+            unsigned int i = atomicAdd(&e.st->n_dirty, 1u);
+            if (i < e.n_blocks) e.dirty_list[i] = blk;
+        }
+    }
+}
+
+// add delta to key in the pair table, inserting the key when absent
+__device__ __forceinline__ void table_add(const EngineDev &e, u64 key, i64 delta) {
+    u64 h = mix64(key) & e.mask;
+    for (unsigned int probe = 0; probe < STBPE_MAX_PROBE; ++probe) {
+        Slot *s = &e.table[h];
+        u64 k = *(volatile u64 *)&s->key;
+        if (k == STBPE_EMPTY) {
+            u64 old = atomicCAS(&s->key, STBPE_EMPTY, key);
+            if (old == STBPE_EMPTY) {
+                atomicAdd(&e.st->n_keys, 1ull);
+                k = key;
+            } else {
+                k = old;
+            }
+        }
+        if (k == key) {
+            atomicAdd((u64 *)&s->count, (u64)delta);
+            mark_dirty(e, h);
+            return;
+        }
+        h = (h + 1) & e.mask;
+    }
+    atomicOr(&e.st->error, STBPE_DERR_TABLE_FULL);
+}
+
+// rank-local delta table (multi-GPU): same probing, first touch recorded for the drain
+__device__ __forceinline__ void ltable_add(const EngineDev &e, u64 key, i64 delta) {
+    u64 h = mix64(key * 0x9E3779B97F4A7C15ULL + 1) & e.lmask;
+    for (unsigned int probe = 0; probe <= (unsigned int)e.lmask; ++probe) {
+        Slot *s = &e.ltable[h];
+        u64 k = *(volatile u64 *)&s->key;
+        if (k == STBPE_EMPTY) {
+            u64 old = atomicCAS(&s->key, STBPE_EMPTY, key);
+            if (old == STBPE_EMPTY) {
+                unsigned int i = atomicAdd(&e.st->n_ltouched, 1u);
+                e.ltouched[i] = (unsigned int)h;  // i <= lmask: one entry per slot
+                k = key;
+            } else {
+                k = old;
+            }
+        }
+        if (k == key) {
+            atomicAdd((u64 *)&s->count, (u64)delta);
+            return;
+        }
+        h = (h + 1) & e.lmask;
+    }
+    atomicOr(&e.st->error, STBPE_DERR_LTABLE_FULL);
+}
+
+template <bool MG>
+__device__ __forceinline__ void sink_add(const EngineDev &e, u64 key, i64 delta) {
+    if (MG)
+        ltable_add(e, key, delta);
+    else
+        table_add(e, key, delta);
+}
+
+// ---------------------------------------------------------------------------------------
+// Per-CTA aggregation table in shared memory: key -> int32 delta.  Inserts that do not
+// find a slot within a few probes go straight to the global sink.
+// ---------------------------------------------------------------------------------------
+struct SmemTable {
+    u64 *keys;
+    int *vals;
+    unsigned int mask;
+};
+
+__device__ __forceinline__ void smem_table_clear(const SmemTable &t) {
+    for (unsigned int i = threadIdx.x; i <= t.mask; i += blockDim.x) {
+        t.keys[i] = STBPE_EMPTY;
+        t.vals[i] = 0;
+    }
+}
+
+__device__ __forceinline__ unsigned int hash32(u64 key) {
+    unsigned int a = (unsigned int)(key >> 32), b = (unsigned int)key;
+    unsigned int h = a * 0x9E3779B1u ^ (b * 0x85EBCA77u + 0x7F4A7C15u);
+    h ^= h >> 15;
+    h *= 0x2C1B3C6Du;
+    h ^= h >> 13;
+    return h;
+}
+
+template <bool MG>
+__device__ __forceinline__ void smem_table_add(const SmemTable &t, const EngineDev &e, u64 key,
+                                               int delta) {
+    unsigned int h = hash32(key) & t.mask;
+#pragma unroll 1
+    for (int probe = 0; probe < 8; ++probe) {
+        u64 k = *(volatile u64 *)&t.keys[h];
+        if (k == STBPE_EMPTY) {
+            u64 old = atomicCAS(&t.keys[h], STBPE_EMPTY, key);
+            k = (old == STBPE_EMPTY) ? key : old;
+        }
+        if (k == key) {
+            atomicAdd(&t.vals[h], delta);
+            return;
+        }
+        h = (h + 1) & t.mask;
+    }
+    sink_add<MG>(e, key, (i64)delta);
+}
+
+template <bool MG>
+__device__ __forceinline__ void smem_table_flush(const SmemTable &t, const EngineDev &e) {
+    for (unsigned int i = threadIdx.x; i <= t.mask; i += blockDim.x) {
+        u64 k = t.keys[i];
+        int v = t.vals[i];
+        if (k != STBPE_EMPTY && v != 0) sink_add<MG>(e, k, (i64)v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Tile records
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ TileRec load_rec(const TileRec *p) {
+    TileRec r;
+    const uint4 *q = reinterpret_cast<const uint4 *>(p);
+    uint4 x = q[0], y = q[1];
+    r.ver = (int)x.x;
+    r.len = (int)x.y;
+    r.head[0] = x.z;
+    r.head[1] = x.w;
+    r.head[2] = y.x;
+    r.tail = y.y;
+    r.pad[0] = r.pad[1] = 0;
+    return r;
+}
+
+// record of `tile` that was current before merge number m; returns its slot index
+__device__ __forceinline__ int current_rec(const EngineDev &e, int tile, int m, TileRec &out) {
+    TileRec r0 = load_rec(&e.recs[2 * tile]);
+    TileRec r1 = load_rec(&e.recs[2 * tile + 1]);
+    bool ok0 = r0.ver >= 0 && r0.ver < m;
+    bool ok1 = r1.ver >= 0 && r1.ver < m;
+    int s = (ok1 && (!ok0 || r1.ver > r0.ver)) ? 1 : 0;
+    out = s ? r1 : r0;
+    if (!ok0 && !ok1) out.len = 0;
+    return s;
+}
+
+// Live tokens around a tile, in stream order: the last live token before it and up to
+// three live tokens after it (STBPE_NONE where the stream ends).  Walks records only.
+__device__ __forceinline__ void gather_halo(const EngineDev &e, int tile, int m, uint32_t &prev,
+                                            uint32_t nxt[3]) {
+    prev = STBPE_NONE;
+    nxt[0] = nxt[1] = nxt[2] = STBPE_NONE;
+    TileRec r;
+    for (int t = tile - 1; t >= 0; --t) {
+        current_rec(e, t, m, r);
+        if (r.len > 0) {
+            prev = r.tail;
+            break;
+        }
+    }
+    int have = 0;
+    for (int t = tile + 1; t < e.n_tiles && have < 3; ++t) {
+        current_rec(e, t, m, r);
+        int take = r.len < 3 ? r.len : 3;
+        for (int i = 0; i < take && have < 3; ++i) nxt[have++] = r.head[i];
+    }
+}

@@ -1,0 +1,671 @@
+// Host side of the C ABI declared in include/stbpe.h: memory, launches, CUDA graphs.
+#include <cub/device/device_radix_sort.cuh>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/stbpe.h"
+#include "kernels.cuh"
+
+#define STBPE_VISIBLE __attribute__((visibility("default")))
+
+struct stbpe_engine {
+    stbpe_config cfg;
+    EngineDev d;
+    i64 max_tokens, n_tokens;
+    int max_tiles;
+    u64 slots;
+    Slot *partial;
+    i64 *cand;
+    u64 lslots;
+    int sm_count;
+    int merge_grid, count_grid, select_grid, refresh_grid;
+    unsigned int merge_slots, count_slots;
+    size_t merge_smem, count_smem;
+    bool recs_stale, counted;
+    cudaGraphExec_t graph;
+    int graph_merges;
+    cudaStream_t graph_stream;
+    bool use_graph;
+    std::string err;
+    std::vector<void *> allocs;
+};
+
+static thread_local std::string g_create_err;
+
+static int fail(stbpe_engine *e, int code, const std::string &msg) {
+    if (e)
+        e->err = msg;
+    else
+        g_create_err = msg;
+    return code;
+}
+
+static int cuda_fail(stbpe_engine *e, cudaError_t c, const char *what) {
+    std::string m = std::string(what) + ": " + cudaGetErrorString(c);
+    if (c == cudaErrorMemoryAllocation) m = "CUDA out of memory (" + m + ")";
+    cudaGetLastError();
+    return fail(e, STBPE_E_CUDA, m);
+}
+
+#define CK(call)                                                  \
+    do {                                                          \
+        cudaError_t c_ = (call);                                  \
+        if (c_ != cudaSuccess) return cuda_fail(e, c_, #call);    \
+    } while (0)
+
+template <typename T>
+static cudaError_t dev_alloc(stbpe_engine *e, T **p, size_t count) {
+    void *q = nullptr;
+    cudaError_t c = cudaMalloc(&q, count * sizeof(T) > 0 ? count * sizeof(T) : 16);
+    if (c == cudaSuccess) {
+        e->allocs.push_back(q);
+        *p = reinterpret_cast<T *>(q);
+    }
+    return c;
+}
+
+static u64 next_pow2(u64 x) {
+    u64 p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+static bool is_device_pointer(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+extern "C" {
+
+STBPE_VISIBLE const char *stbpe_version(void) { return "stbpe 0.1 (sm_100a)"; }
+
+STBPE_VISIBLE const char *stbpe_last_error(const stbpe_engine *e) {
+    return e ? e->err.c_str() : g_create_err.c_str();
+}
+
+STBPE_VISIBLE int stbpe_destroy(stbpe_engine *e) {
+    if (!e) return STBPE_OK;
+    cudaSetDevice(e->cfg.device);
+    if (e->graph) cudaGraphExecDestroy(e->graph);
+    for (void *p : e->allocs) cudaFree(p);
+    delete e;
+    return STBPE_OK;
+}
+
+static int reset_state(stbpe_engine *e, cudaStream_t s) {
+    DevState h;
+    memset(&h, 0, sizeof(h));
+    h.base_vocab = e->cfg.base_vocab;
+    CK(cudaMemcpyAsync(e->d.st, &h, sizeof(h), cudaMemcpyHostToDevice, s));
+    CK(cudaStreamSynchronize(s));
+    e->n_tokens = 0;
+    e->d.n_tiles = 0;
+    e->recs_stale = true;
+    e->counted = false;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
+    if (!out || !cfg) return fail(nullptr, STBPE_E_BADARG, "null argument");
+    if (cfg->max_tokens < 0 || cfg->max_merges < 0 || cfg->base_vocab < 0 || cfg->world_size < 1 ||
+        cfg->rank < 0 || cfg->rank >= cfg->world_size)
+        return fail(nullptr, STBPE_E_BADARG, "invalid configuration");
+    if ((i64)cfg->base_vocab + (i64)cfg->max_merges >= 0x7FFFFFFFll)
+        return fail(nullptr, STBPE_E_ID_OVERFLOW, "Token id overflow: ids must stay below 2^31-1");
+    stbpe_engine *e = new stbpe_engine();
+    e->cfg = *cfg;
+    e->graph = nullptr;
+    e->graph_merges = 0;
+    e->use_graph = getenv("STBPE_NO_GRAPH") == nullptr;
+    memset(&e->d, 0, sizeof(e->d));
+    auto bail = [&](int code) {
+        g_create_err = e->err;
+        stbpe_destroy(e);
+        return code;
+    };
+    cudaError_t c = cudaSetDevice(cfg->device);
+    if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaSetDevice"));
+    cudaDeviceProp prop;
+    c = cudaGetDeviceProperties(&prop, cfg->device);
+    if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaGetDeviceProperties"));
+    e->sm_count = prop.multiProcessorCount;
+
+    e->max_tokens = cfg->max_tokens;
+    e->max_tiles = (int)((cfg->max_tokens + STBPE_TILE - 1) / STBPE_TILE);
+    if (e->max_tiles < 1) e->max_tiles = 1;
+    u64 slots = cfg->table_slots > 0 ? (u64)cfg->table_slots : (u64)cfg->max_tokens / 4;
+    if (cfg->table_slots <= 0) {
+        if (slots < (1ull << 20)) slots = 1ull << 20;
+        if (slots > (1ull << 27)) slots = 1ull << 27;
+    }
+    slots = next_pow2(slots < (u64)STBPE_BLK ? STBPE_BLK : slots);
+    e->slots = slots;
+    e->d.mask = slots - 1;
+    e->d.n_blocks = (unsigned int)(slots / STBPE_BLK);
+    e->d.world = cfg->world_size;
+    e->d.rank = cfg->rank;
+
+#define ALLOC(ptr, n)                                                  \
+    if ((c = dev_alloc(e, &(ptr), (size_t)(n))) != cudaSuccess) return bail(cuda_fail(e, c, "cudaMalloc " #ptr))
+    ALLOC(e->d.tiles, (size_t)e->max_tiles * STBPE_TILE);
+    ALLOC(e->d.recs, (size_t)e->max_tiles * 2);
+    ALLOC(e->d.table, slots);
+    ALLOC(e->d.blockmax, e->d.n_blocks);
+    ALLOC(e->d.dirty_flag, e->d.n_blocks);
+    ALLOC(e->d.dirty_list, e->d.n_blocks);
+    ALLOC(e->d.st, 1);
+    ALLOC(e->d.merges, (size_t)2 * (cfg->max_merges + 1));
+    ALLOC(e->d.merge_counts, (size_t)cfg->max_merges + 1);
+    ALLOC(e->d.live_before, (size_t)cfg->max_merges + 1);
+    ALLOC(e->partial, 4096);
+    ALLOC(e->cand, 2);
+    if (cfg->world_size > 1) {
+        e->lslots = 1ull << 22;
+        e->d.lmask = e->lslots - 1;
+        e->d.cap_per_peer = (i64)(1 << 18);
+        ALLOC(e->d.ltable, e->lslots);
+        ALLOC(e->d.ltouched, e->lslots + 1);
+        ALLOC(e->d.outbox, (size_t)cfg->world_size * (e->d.cap_per_peer + 1));
+        ALLOC(e->d.inbox, (size_t)cfg->world_size * (e->d.cap_per_peer + 1));
+        c = cudaMemset(e->d.ltable, 0xFF, e->lslots * sizeof(Slot));
+        if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaMemset ltable"));
+        // counts of the local table must start at zero (keys at EMPTY = all ones)
+        std::vector<Slot> init(1 << 16);
+        for (auto &s : init) { s.key = STBPE_EMPTY; s.count = 0; }
+        for (u64 off = 0; off < e->lslots; off += init.size()) {
+            c = cudaMemcpy(e->d.ltable + off, init.data(), init.size() * sizeof(Slot), cudaMemcpyHostToDevice);
+            if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaMemcpy ltable"));
+        }
+    }
+#undef ALLOC
+    c = cudaMemset(e->d.dirty_flag, 0, e->d.n_blocks * sizeof(unsigned int));
+    if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaMemset"));
+
+    // launch geometry: persistent CTAs, a whole number per SM
+    e->merge_slots = 2048;
+    e->count_slots = 8192;
+    e->merge_smem = (STBPE_TILE + 8) * sizeof(uint32_t) + (size_t)e->merge_slots * 12;
+    e->count_smem = (STBPE_TILE + 8) * sizeof(uint32_t) + (size_t)e->count_slots * 12;
+    int occ = 0;
+#define SETUP(kern, smem, grid)                                                                         \
+    c = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem));           \
+    if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaFuncSetAttribute"));                         \
+    c = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, STBPE_NT, smem);                      \
+    if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaOccupancyMaxActiveBlocksPerMultiprocessor")); \
+    grid = e->sm_count * (occ > 0 ? occ : 1)
+    int g1 = 0, g2 = 0;
+    SETUP(merge_kernel<false>, e->merge_smem, e->merge_grid);
+    SETUP(merge_kernel<true>, e->merge_smem, g1);
+    SETUP(count_kernel<false>, e->count_smem, e->count_grid);
+    SETUP(count_kernel<true>, e->count_smem, g2);
+    if (g1 < e->merge_grid) e->merge_grid = g1;
+    if (g2 < e->count_grid) e->count_grid = g2;
+#undef SETUP
+    e->select_grid = e->sm_count;
+    e->refresh_grid = e->sm_count * 4;
+    int rc = reset_state(e, 0);
+    if (rc != STBPE_OK) return bail(rc);
+    *out = e;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_reset(stbpe_engine *e) {
+    if (!e) return STBPE_E_BADARG;
+    CK(cudaSetDevice(e->cfg.device));
+    return reset_state(e, 0);
+}
+
+static int append_common(stbpe_engine *e, const void *data, i64 n, size_t elem, const i64 *row_offsets,
+                         i64 n_rows, cudaStream_t s) {
+    if (n < 0 || n_rows < 0 || (n > 0 && !data)) return fail(e, STBPE_E_BADARG, "bad append arguments");
+    if (e->n_tokens + n > e->max_tokens)
+        return fail(e, STBPE_E_CAPACITY, "token stream capacity exceeded");
+    CK(cudaSetDevice(e->cfg.device));
+    if (n == 0) return STBPE_OK;
+    const void *src = data;
+    void *staged = nullptr;
+    if (!is_device_pointer(data)) {
+        CK(cudaMallocAsync(&staged, (size_t)n * elem, s));
+        CK(cudaMemcpyAsync(staged, data, (size_t)n * elem, cudaMemcpyHostToDevice, s));
+        src = staged;
+    }
+    uint32_t *dst = e->d.tiles + e->n_tokens;
+    unsigned int *bad = &e->d.st->error;
+    if (elem == 1) {
+        i64 blocks = (n / 16 + 255) / 256 + 1;
+        if (blocks > 65535 * 16) blocks = 65535 * 16;
+        pack_bytes_kernel<<<(unsigned int)blocks, 256, 0, s>>>((const uint8_t *)src, n, dst);
+    } else {
+        i64 blocks = (n + 255) / 256;
+        if (blocks > 65535 * 16) blocks = 65535 * 16;
+        pack_ids_kernel<<<(unsigned int)blocks, 256, 0, s>>>((const int32_t *)src, n, dst, bad);
+    }
+    CK(cudaGetLastError());
+    // row starts
+    std::vector<i64> single = {0, n};
+    const i64 *off = row_offsets;
+    i64 rows = n_rows;
+    if (!off) {
+        off = single.data();
+        rows = 1;
+    } else {
+        if (off[0] != 0 || off[rows] != n) {
+            if (staged) cudaFreeAsync(staged, s);
+            return fail(e, STBPE_E_BADARG, "row_offsets must start at 0 and end at n");
+        }
+    }
+    i64 *doff = nullptr;
+    CK(cudaMallocAsync((void **)&doff, (size_t)(rows + 1) * sizeof(i64), s));
+    CK(cudaMemcpyAsync(doff, off, (size_t)(rows + 1) * sizeof(i64), cudaMemcpyHostToDevice, s));
+    mark_row_starts_kernel<<<(unsigned int)((rows + 255) / 256), 256, 0, s>>>(doff, rows, dst);
+    CK(cudaGetLastError());
+    CK(cudaFreeAsync(doff, s));
+    if (staged) CK(cudaFreeAsync(staged, s));
+    // the host offsets (and a host source) must stay valid until the copies ran
+    CK(cudaStreamSynchronize(s));
+    e->n_tokens += n;
+    e->recs_stale = true;
+    e->counted = false;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_append_bytes(stbpe_engine *e, const uint8_t *data, int64_t n,
+                                     const int64_t *row_offsets, int64_t n_rows, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    return append_common(e, data, n, 1, (const i64 *)row_offsets, n_rows, (cudaStream_t)stream);
+}
+
+STBPE_VISIBLE int stbpe_append_ids(stbpe_engine *e, const int32_t *ids, int64_t n,
+                                   const int64_t *row_offsets, int64_t n_rows, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    return append_common(e, ids, n, 4, (const i64 *)row_offsets, n_rows, (cudaStream_t)stream);
+}
+
+static int check_device_error(stbpe_engine *e, cudaStream_t s) {
+    unsigned int err = 0;
+    CK(cudaMemcpyAsync(&err, &e->d.st->error, sizeof(err), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    if (err & STBPE_DERR_BAD_ID)
+        return fail(e, STBPE_E_ID_OVERFLOW, "Token id overflow: ids must be in [0, 2^31-2]");
+    if (err & STBPE_DERR_TABLE_FULL)
+        return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (pair table full)");
+    if (err & STBPE_DERR_OUTBOX_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (delta outbox full)");
+    if (err & STBPE_DERR_LTABLE_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (local delta table full)");
+    if (err & STBPE_DERR_KEY_MISSING) return fail(e, STBPE_E_STATE, "selected pair missing from the pair table");
+    return STBPE_OK;
+}
+
+static int prepare_stream_state(stbpe_engine *e, cudaStream_t s) {
+    if (e->recs_stale) {
+        int rc = check_device_error(e, s);  // id range flag from the pack kernels
+        if (rc != STBPE_OK) return rc;
+        e->d.n_tiles = (int)((e->n_tokens + STBPE_TILE - 1) / STBPE_TILE);
+        if (e->d.n_tiles > 0) {
+            init_recs_kernel<<<(e->d.n_tiles + 255) / 256, 256, 0, s>>>(e->d, e->n_tokens);
+            CK(cudaGetLastError());
+        }
+        DevState h;
+        memset(&h, 0, sizeof(h));
+        h.base_vocab = e->cfg.base_vocab;
+        h.n_live = e->n_tokens;
+        CK(cudaMemcpyAsync(e->d.st, &h, sizeof(h), cudaMemcpyHostToDevice, s));
+        CK(cudaStreamSynchronize(s));
+        e->recs_stale = false;
+    }
+    return STBPE_OK;
+}
+
+static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
+    int rc = prepare_stream_state(e, s);
+    if (rc != STBPE_OK) return rc;
+    clear_table_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    CK(cudaMemsetAsync(e->d.dirty_flag, 0, e->d.n_blocks * sizeof(unsigned int), s));
+    CK(cudaMemsetAsync(&e->d.st->n_dirty, 0, sizeof(unsigned int), s));
+    CK(cudaMemsetAsync(&e->d.st->n_keys, 0, sizeof(u64), s));
+    if (e->d.n_tiles > 0) {
+        int grid = e->count_grid < e->d.n_tiles ? e->count_grid : e->d.n_tiles;
+        if (mg)
+            count_kernel<true><<<grid, STBPE_NT, e->count_smem, s>>>(e->d, e->count_slots);
+        else
+            count_kernel<false><<<grid, STBPE_NT, e->count_smem, s>>>(e->d, e->count_slots);
+        CK(cudaGetLastError());
+    }
+    return STBPE_OK;
+}
+
+static int launch_refresh(stbpe_engine *e, int all, cudaStream_t s) {
+    refresh_kernel<<<e->refresh_grid, 256, 0, s>>>(e->d, all);
+    CK(cudaGetLastError());
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_count_initial(stbpe_engine *e, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (e->cfg.world_size > 1) return fail(e, STBPE_E_STATE, "use stbpe_mg_count_local on a multi-rank engine");
+    int rc = launch_count(e, false, s);
+    if (rc != STBPE_OK) return rc;
+    rc = launch_refresh(e, 1, s);
+    if (rc != STBPE_OK) return rc;
+    e->counted = true;
+    return check_device_error(e, s);
+}
+
+STBPE_VISIBLE int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *count, int64_t *n_ties,
+                                    void *stream) {
+    if (!e || !key || !count) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->counted) return fail(e, STBPE_E_STATE, "count the pairs before selecting");
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 0, e->partial, e->cand);
+    CK(cudaGetLastError());
+    if (n_ties) {
+        CK(cudaMemsetAsync(&e->d.st->peek_ties, 0, sizeof(i64), s));
+        count_ties_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d);
+        CK(cudaGetLastError());
+    }
+    DevState h;
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    *key = h.peek_count > 0 ? h.peek_key : 0;
+    *count = h.peek_count;
+    if (n_ties) *n_ties = h.peek_count > 0 ? h.peek_ties : 0;
+    return STBPE_OK;
+}
+
+static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s) {
+    if (e->d.n_tiles > 0) {
+        int grid = e->merge_grid < e->d.n_tiles ? e->merge_grid : e->d.n_tiles;
+        if (mg)
+            merge_kernel<true><<<grid, STBPE_NT, e->merge_smem, s>>>(e->d, e->merge_slots);
+        else
+            merge_kernel<false><<<grid, STBPE_NT, e->merge_smem, s>>>(e->d, e->merge_slots);
+        CK(cudaGetLastError());
+    }
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_apply_merge(stbpe_engine *e, int32_t a, int32_t b, int32_t new_id,
+                                    int64_t *n_matches, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->counted) return fail(e, STBPE_E_STATE, "count the pairs before merging");
+    if (e->cfg.world_size > 1) return fail(e, STBPE_E_STATE, "single-rank entry point");
+    if (a < 0 || b < 0 || new_id < 0 || a == 0x7FFFFFFF || b == 0x7FFFFFFF || new_id == 0x7FFFFFFF)
+        return fail(e, STBPE_E_ID_OVERFLOW, "Token id overflow: ids must be in [0, 2^31-2]");
+    DevState h;
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    if (h.merges_done >= e->cfg.max_merges) return fail(e, STBPE_E_CAPACITY, "merge log full");
+    force_merge_kernel<<<1, 1, 0, s>>>(e->d, a, b, new_id);
+    CK(cudaGetLastError());
+    int rc = launch_merge(e, false, s);
+    if (rc != STBPE_OK) return rc;
+    rc = launch_refresh(e, 0, s);
+    if (rc != STBPE_OK) return rc;
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    if (n_matches) *n_matches = h.n_matches;
+    return check_device_error(e, s);
+}
+
+__global__ void set_target_kernel(EngineDev e, int target) {
+    e.st->target = target;
+    e.st->stopped = 0;
+    e.st->stop_reason = 0;
+    e.st->n_matches = 0;
+}
+
+static int enqueue_iteration(stbpe_engine *e, cudaStream_t s) {
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+    CK(cudaGetLastError());
+    int rc = launch_merge(e, false, s);
+    if (rc != STBPE_OK) return rc;
+    return launch_refresh(e, 0, s);
+}
+
+STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
+    if (!e || n_merges < 0) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->counted) return fail(e, STBPE_E_STATE, "count the pairs before training");
+    if (e->cfg.world_size > 1) return fail(e, STBPE_E_STATE, "single-rank entry point");
+    DevState h;
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    i64 target = (i64)h.merges_done + n_merges;
+    if (target > e->cfg.max_merges) target = e->cfg.max_merges;
+    set_target_kernel<<<1, 1, 0, s>>>(e->d, (int)target);
+    CK(cudaGetLastError());
+    int todo = (int)(target - h.merges_done);
+    const int G = 32;
+    if (e->use_graph && todo >= G) {
+        // the kernels take all their work from device state, so one captured batch of G
+        // iterations is replayed; iterations past a stop rule return immediately
+        if (e->graph && (e->graph_merges != e->d.n_tiles)) {
+            cudaGraphExecDestroy(e->graph);
+            e->graph = nullptr;
+        }
+        if (!e->graph) {
+            cudaStream_t cs;
+            CK(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
+            cudaGraph_t g;
+            CK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+            int rc = STBPE_OK;
+            for (int i = 0; i < G && rc == STBPE_OK; ++i) rc = enqueue_iteration(e, cs);
+            cudaError_t ce = cudaStreamEndCapture(cs, &g);
+            if (rc != STBPE_OK) {
+                cudaStreamDestroy(cs);
+                return rc;
+            }
+            if (ce != cudaSuccess) {
+                cudaStreamDestroy(cs);
+                return cuda_fail(e, ce, "cudaStreamEndCapture");
+            }
+            ce = cudaGraphInstantiate(&e->graph, g, 0);
+            cudaGraphDestroy(g);
+            cudaStreamDestroy(cs);
+            if (ce != cudaSuccess) return cuda_fail(e, ce, "cudaGraphInstantiate");
+            e->graph_merges = e->d.n_tiles;  // the capture froze n_tiles and the grids
+        }
+        while (todo > 0) {
+            CK(cudaGraphLaunch(e->graph, s));
+            todo -= G;
+        }
+    } else {
+        for (int i = 0; i < todo; ++i) {
+            int rc = enqueue_iteration(e, s);
+            if (rc != STBPE_OK) return rc;
+        }
+    }
+    // one more selection decides the stop reason without applying anything when the target is reached
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(s));
+    return check_device_error(e, s);
+}
+
+STBPE_VISIBLE int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *stream) {
+    if (!e || !out) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    DevState h;
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    out->merges_done = h.merges_done;
+    out->stop_reason = h.stopped ? h.stop_reason : STBPE_RUNNING;
+    out->live_tokens = e->recs_stale ? e->n_tokens : h.n_live;
+    out->table_keys = (i64)h.n_keys;
+    out->table_slots = (i64)e->slots;
+    out->device_error = h.error;
+    out->n_tiles = e->d.n_tiles;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_get_merges(stbpe_engine *e, int32_t first, int32_t n, int32_t *merges,
+                                   int64_t *counts, int64_t *live_before) {
+    if (!e || first < 0 || n < 0 || first + n > e->cfg.max_merges || (n > 0 && !merges))
+        return fail(e, STBPE_E_BADARG, "bad merge range");
+    CK(cudaSetDevice(e->cfg.device));
+    if (n == 0) return STBPE_OK;
+    CK(cudaMemcpy(merges, e->d.merges + 2 * first, (size_t)n * 2 * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    if (counts) CK(cudaMemcpy(counts, e->d.merge_counts + first, (size_t)n * sizeof(i64), cudaMemcpyDeviceToHost));
+    if (live_before) CK(cudaMemcpy(live_before, e->d.live_before + first, (size_t)n * sizeof(i64), cudaMemcpyDeviceToHost));
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_export_histogram(stbpe_engine *e, uint64_t *keys, int64_t *counts, int64_t cap,
+                                         int64_t *n_out, void *stream) {
+    if (!e || !n_out || cap < 0) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    u64 *tk = nullptr;
+    i64 *tc = nullptr;
+    CK(cudaMallocAsync((void **)&tk, (size_t)(cap > 0 ? cap : 1) * sizeof(u64), s));
+    CK(cudaMallocAsync((void **)&tc, (size_t)(cap > 0 ? cap : 1) * sizeof(i64), s));
+    CK(cudaMemsetAsync(&e->d.st->export_n, 0, sizeof(i64), s));
+    export_table_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, tk, tc, cap);
+    CK(cudaGetLastError());
+    i64 n = 0;
+    CK(cudaMemcpyAsync(&n, &e->d.st->export_n, sizeof(i64), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    *n_out = n;
+    int rc = STBPE_OK;
+    if (n > cap) {
+        rc = fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded");
+    } else if (n > 0) {
+        size_t tmp_bytes = 0;
+        cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, tk, (u64 *)keys, tc, (i64 *)counts, (int)n, 0, 64, s);
+        void *tmp = nullptr;
+        CK(cudaMallocAsync(&tmp, tmp_bytes ? tmp_bytes : 16, s));
+        cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, tk, (u64 *)keys, tc, (i64 *)counts, (int)n, 0, 64, s);
+        CK(cudaGetLastError());
+        CK(cudaFreeAsync(tmp, s));
+    }
+    CK(cudaFreeAsync(tk, s));
+    CK(cudaFreeAsync(tc, s));
+    CK(cudaStreamSynchronize(s));
+    return rc;
+}
+
+STBPE_VISIBLE int stbpe_export_stream(stbpe_engine *e, int32_t *ids, int64_t cap, int64_t *n_out,
+                                      void *stream) {
+    if (!e || !n_out) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    int rc = prepare_stream_state(e, s);
+    if (rc != STBPE_OK) return rc;
+    const int nt = e->d.n_tiles;
+    *n_out = 0;
+    if (nt == 0) return STBPE_OK;
+    i64 *dl = nullptr;
+    CK(cudaMallocAsync((void **)&dl, (size_t)(nt + 1) * sizeof(i64), s));
+    tile_lens_kernel<<<(nt + 255) / 256, 256, 0, s>>>(e->d, dl);
+    CK(cudaGetLastError());
+    std::vector<i64> lens(nt + 1), off(nt + 1);
+    CK(cudaMemcpyAsync(lens.data(), dl, (size_t)nt * sizeof(i64), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    off[0] = 0;
+    for (int t = 0; t < nt; ++t) off[t + 1] = off[t] + lens[t];
+    *n_out = off[nt];
+    if (off[nt] > cap) {
+        cudaFreeAsync(dl, s);
+        return fail(e, STBPE_E_CAPACITY, "export buffer too small");
+    }
+    CK(cudaMemcpyAsync(dl, off.data(), (size_t)(nt + 1) * sizeof(i64), cudaMemcpyHostToDevice, s));
+    export_stream_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d, dl, ids);
+    CK(cudaGetLastError());
+    CK(cudaFreeAsync(dl, s));
+    CK(cudaStreamSynchronize(s));
+    return STBPE_OK;
+}
+
+// ------------------------------------------------------------------------------- multi-GPU
+STBPE_VISIBLE int stbpe_mg_buffers(stbpe_engine *e, void **outbox, void **inbox, int64_t *cap_per_peer,
+                                   int64_t *bytes_per_peer) {
+    if (!e) return STBPE_E_BADARG;
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    if (outbox) *outbox = e->d.outbox;
+    if (inbox) *inbox = e->d.inbox;
+    if (cap_per_peer) *cap_per_peer = e->d.cap_per_peer;
+    if (bytes_per_peer) *bytes_per_peer = (e->d.cap_per_peer + 1) * (i64)sizeof(Slot);
+    return STBPE_OK;
+}
+
+static int launch_drain(stbpe_engine *e, cudaStream_t s) {
+    outbox_reset_kernel<<<1, 64, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    drain_ltable_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    ltouched_reset_kernel<<<1, 1, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_count_local(stbpe_engine *e, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    int rc = launch_count(e, true, s);
+    if (rc != STBPE_OK) return rc;
+    rc = launch_drain(e, s);
+    if (rc != STBPE_OK) return rc;
+    e->counted = true;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_merge_local(stbpe_engine *e, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    int rc = launch_merge(e, true, s);
+    if (rc != STBPE_OK) return rc;
+    return launch_drain(e, s);
+}
+
+STBPE_VISIBLE int stbpe_mg_apply_inbox(stbpe_engine *e, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    apply_inbox_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    return launch_refresh(e, 0, s);
+}
+
+STBPE_VISIBLE int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev, void *stream) {
+    if (!e || !cand_dev) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 2, e->partial, (i64 *)cand_dev);
+    CK(cudaGetLastError());
+    return STBPE_OK;
+}
+
+__global__ void set_target_if_unset_kernel(EngineDev e, int target) { e.st->target = target; }
+
+STBPE_VISIBLE int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev, void *stream) {
+    if (!e || !all_cands_dev) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    set_target_if_unset_kernel<<<1, 1, 0, s>>>(e->d, e->cfg.max_merges);
+    commit_kernel<<<1, 1, 0, s>>>(e->d, (const i64 *)all_cands_dev);
+    CK(cudaGetLastError());
+    return STBPE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,576 @@
+// Kernels of the BPE merge-loop engine (sm_100a).  See common.cuh for the data layout.
+#pragma once
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// K1  pack: bytes / ids -> uint32 stream words, row-start flags, tile records
+// ---------------------------------------------------------------------------------------
+// identity byte -> id map of the reference's packer (gpu_tokenizer/cpu_packer.py:17-26)
+__global__ void pack_bytes_kernel(const uint8_t *__restrict__ src, i64 n, uint32_t *__restrict__ dst) {
+    i64 i = ((i64)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+    i64 stride = (i64)gridDim.x * blockDim.x * 16;
+    bool aligned = ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0;
+    for (; i < n; i += stride) {
+        if (aligned && i + 16 <= n) {
+            uint4 v = *reinterpret_cast<const uint4 *>(src + i);
+            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = w[q] & 0xFF;
+                o.y = (w[q] >> 8) & 0xFF;
+                o.z = (w[q] >> 16) & 0xFF;
+                o.w = w[q] >> 24;
+                *reinterpret_cast<uint4 *>(dst + i + 4 * q) = o;
+            }
+        } else {
+            for (i64 k = i; k < n && k < i + 16; ++k) dst[k] = src[k];
+        }
+    }
+}
+
+__global__ void pack_ids_kernel(const int32_t *__restrict__ src, i64 n, uint32_t *__restrict__ dst,
+                                unsigned int *bad) {
+    i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    i64 stride = (i64)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        int32_t v = src[i];
+        if (v < 0 || v == 0x7FFFFFFF) atomicOr(bad, STBPE_DERR_BAD_ID);  // ids must leave bit 31 and NONE free
+        dst[i] = (uint32_t)v & STBPE_IDMASK;
+    }
+}
+
+__global__ void mark_row_starts_kernel(const i64 *__restrict__ off, i64 n_rows, uint32_t *stream) {
+    i64 r = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n_rows && off[r] < off[r + 1]) stream[off[r]] |= STBPE_FLAG;
+}
+
+__global__ void init_recs_kernel(EngineDev e, i64 n_tokens) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= e.n_tiles) return;
+    i64 base = (i64)t * STBPE_TILE;
+    i64 rem = n_tokens - base;
+    int len = rem >= STBPE_TILE ? STBPE_TILE : (int)rem;
+    TileRec r;
+    r.ver = 0;
+    r.len = len;
+    for (int i = 0; i < 3; ++i) r.head[i] = i < len ? e.tiles[base + i] : STBPE_NONE;
+    r.tail = len > 0 ? e.tiles[base + len - 1] : STBPE_NONE;
+    r.pad[0] = r.pad[1] = 0;
+    e.recs[2 * t] = r;
+    r.ver = -1;
+    r.len = 0;
+    e.recs[2 * t + 1] = r;
+}
+
+__global__ void clear_table_kernel(EngineDev e) {
+    u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+    u64 stride = (u64)gridDim.x * blockDim.x;
+    for (; i <= e.mask; i += stride) {
+        Slot s;
+        s.key = STBPE_EMPTY;
+        s.count = 0;
+        e.table[i] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// K2  full adjacent-pair histogram (gpu_tokenizer/utils.py:558-635 without the sort)
+// Persistent CTAs walk tiles; every countable pair adds +1 into the CTA's shared-memory
+// table, which is flushed into the pair table (or the rank-local delta table) at the end.
+// ---------------------------------------------------------------------------------------
+template <bool MG>
+__global__ void __launch_bounds__(STBPE_NT, 2) count_kernel(EngineDev e, unsigned int smem_slots) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint32_t *s_tok = reinterpret_cast<uint32_t *>(smem_raw);
+    SmemTable tab;
+    tab.keys = reinterpret_cast<u64 *>(smem_raw + (STBPE_TILE + 8) * sizeof(uint32_t));
+    tab.vals = reinterpret_cast<int *>(tab.keys + smem_slots);
+    tab.mask = smem_slots - 1;
+    smem_table_clear(tab);
+    const int m = 0x7FFFFFFF;  // any record version is "before" this
+    const int tid = threadIdx.x;
+    __syncthreads();
+    for (int tile = blockIdx.x; tile < e.n_tiles; tile += gridDim.x) {
+        TileRec rec;
+        current_rec(e, tile, m, rec);
+        const int len = rec.len;
+        if (len == 0) continue;
+        const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
+        for (int i = tid * 4; i < len; i += STBPE_NT * 4)
+            *reinterpret_cast<uint4 *>(s_tok + i) = *reinterpret_cast<const uint4 *>(g + i);
+        uint32_t prev, nxt[3];
+        if (tid == 0) gather_halo(e, tile, m, prev, nxt);
+        __syncthreads();
+        if (tid == 0) s_tok[len] = nxt[0];
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < STBPE_IPT; ++j) {
+            int p = j * STBPE_NT + tid;
+            if (p < len) {
+                uint32_t t0 = s_tok[p], t1 = s_tok[p + 1];
+                if (!(t1 & STBPE_FLAG)) {
+                    u64 key = ((u64)(t0 & STBPE_IDMASK) << 32) | (u64)t1;
+                    smem_table_add<MG>(tab, e, key, 1);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    smem_table_flush<MG>(tab, e);
+}
+
+// ---------------------------------------------------------------------------------------
+// K3  one merge: find + rewrite + in-tile compaction + delta counts
+//
+// With M[i] = (id[i]==a && id[i+1]==b && token i+1 does not start a row) evaluated on
+// the pre-merge stream (gpu_tokenizer/utils.py:520-527), token i is dropped when M[i-1]
+// and becomes `new` when M[i] (utils.py:529-531).  The histogram of the result equals
+// the old histogram plus these local terms (x = live token before, y = after):
+//   every countable input pair (i,i+1) with M[i-1] | M[i] | M[i+1] ... -1, except the
+//     merged pair itself, whose table entry is zeroed when the merge is selected;
+//   a != b : M[i]            ... +1 (new, out[i+2]) if i+2 is in the row,
+//                                   out[i+2] = new when M[i+2]
+//            !M[i-1] & !M[i] ... +1 (id[i], new) when M[i+1]
+//   a == b : !M[i-1] & !M[i] ... +1 (id[i], new) when M[i+1]
+//            M[i-1] & !M[i]  ... +1 (new, id[i+1]) if i+1 is in the row   (tail of a run:
+//                                   the whole run collapses into ONE new token)
+// which is what a full recount of the rewritten rows gives.
+// ---------------------------------------------------------------------------------------
+template <bool MG>
+__global__ void __launch_bounds__(STBPE_NT, 2) merge_kernel(EngineDev e, unsigned int smem_slots) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int s_wcnt[STBPE_IPT * STBPE_NW];
+    __shared__ uint32_t s_prev;
+    __shared__ int s_total;
+
+    DevState *st = e.st;
+    if (st->stopped) return;
+    const uint32_t a = (uint32_t)st->cur_a, b = (uint32_t)st->cur_b, nw = (uint32_t)st->cur_new;
+    const int m = st->merges_done;  // number of this merge (>= 1)
+    const bool same = (a == b);
+
+    uint32_t *s_tok = reinterpret_cast<uint32_t *>(smem_raw);
+    SmemTable tab;
+    tab.keys = reinterpret_cast<u64 *>(smem_raw + (STBPE_TILE + 8) * sizeof(uint32_t));
+    tab.vals = reinterpret_cast<int *>(tab.keys + smem_slots);
+    tab.mask = smem_slots - 1;
+    smem_table_clear(tab);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    i64 removed = 0, matches = 0;
+    __syncthreads();
+
+    for (int tile = blockIdx.x; tile < e.n_tiles; tile += gridDim.x) {
+        TileRec rec;
+        const int cur_slot = current_rec(e, tile, m, rec);
+        const int len = rec.len;
+        if (len == 0) continue;
+        uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
+        for (int i = tid * 4; i < len; i += STBPE_NT * 4)
+            *reinterpret_cast<uint4 *>(s_tok + i) = *reinterpret_cast<const uint4 *>(g + i);
+        uint32_t prev, nxt[3];
+        if (tid == 0) gather_halo(e, tile, m, prev, nxt);
+        __syncthreads();
+        if (tid == 0) {
+            s_prev = prev;
+            s_tok[len] = nxt[0];
+            s_tok[len + 1] = nxt[1];
+            s_tok[len + 2] = nxt[2];
+        }
+        __syncthreads();
+
+        uint32_t outv[STBPE_IPT];
+        unsigned int surv = 0;
+        int changed = 0, my_matches = 0;
+#pragma unroll
+        for (int j = 0; j < STBPE_IPT; ++j) {
+            const int p = j * STBPE_NT + tid;
+            outv[j] = 0;
+            if (p < len) {
+                const uint32_t tm1 = p ? s_tok[p - 1] : s_prev;
+                const uint32_t t0 = s_tok[p], t1 = s_tok[p + 1], t2 = s_tok[p + 2], t3 = s_tok[p + 3];
+                const uint32_t i0 = t0 & STBPE_IDMASK;
+                // a token following by a row start never matches: t1 == b is a compare of the
+                // whole word, so the flag bit must be clear
+                const bool M0 = (i0 == a) && (t1 == b);
+                const bool D0 = ((tm1 & STBPE_IDMASK) == a) && (t0 == b);
+                const bool M1 = ((t1 & STBPE_IDMASK) == a) && (t2 == b);
+                const bool pair01 = !(t1 & STBPE_FLAG);
+                if (pair01 && !M0 && (D0 || M1))
+                    smem_table_add<MG>(tab, e, ((u64)i0 << 32) | (u64)t1, -1);
+                if (!same) {
+                    if (M0) {
+                        if (!(t2 & STBPE_FLAG)) {
+                            const bool M2 = (t2 == a) && (t3 == b);
+                            smem_table_add<MG>(tab, e, ((u64)nw << 32) | (u64)(M2 ? nw : t2), 1);
+                        }
+                    } else if (!D0 && pair01 && M1) {
+                        smem_table_add<MG>(tab, e, ((u64)i0 << 32) | (u64)nw, 1);
+                    }
+                } else {
+                    if (!M0 && !D0) {
+                        if (pair01 && M1) smem_table_add<MG>(tab, e, ((u64)i0 << 32) | (u64)nw, 1);
+                    } else if (D0 && !M0) {
+                        if (pair01) smem_table_add<MG>(tab, e, ((u64)nw << 32) | (u64)t1, 1);
+                    }
+                }
+                outv[j] = M0 ? (nw | (t0 & STBPE_FLAG)) : t0;
+                if (!D0) surv |= 1u << j;
+                changed |= (int)(M0 | D0);
+                my_matches += (int)M0;
+            }
+        }
+        matches += my_matches;
+        // barrier: every thread has read its neighbourhood; also the "anything to do" vote
+        if (!__syncthreads_or(changed)) continue;
+
+        unsigned int bal[STBPE_IPT];
+#pragma unroll
+        for (int j = 0; j < STBPE_IPT; ++j) {
+            bal[j] = __ballot_sync(0xFFFFFFFFu, (surv >> j) & 1u);
+            if (lane == 0) s_wcnt[j * STBPE_NW + warp] = __popc(bal[j]);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // exclusive scan of the IPT*NW (=128) per-warp counts, 4 per lane
+            int v[4], sum = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                v[q] = s_wcnt[lane * 4 + q];
+                sum += v[q];
+            }
+            int incl = sum;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                int n = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                if (lane >= d) incl += n;
+            }
+            int run = incl - sum;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                s_wcnt[lane * 4 + q] = run;
+                run += v[q];
+            }
+            if (lane == 31) s_total = incl;
+        }
+        __syncthreads();
+        const unsigned int lt = (1u << lane) - 1u;
+#pragma unroll
+        for (int j = 0; j < STBPE_IPT; ++j)
+            if ((surv >> j) & 1u) s_tok[s_wcnt[j * STBPE_NW + warp] + __popc(bal[j] & lt)] = outv[j];
+        __syncthreads();
+        const int newlen = s_total;
+        for (int i = tid * 4; i < newlen; i += STBPE_NT * 4)
+            *reinterpret_cast<uint4 *>(g + i) = *reinterpret_cast<const uint4 *>(s_tok + i);
+        if (tid == 0) {
+            TileRec *dst = &e.recs[2 * tile + (cur_slot ^ 1)];
+            dst->len = newlen;
+            for (int i = 0; i < 3; ++i) dst->head[i] = i < newlen ? s_tok[i] : STBPE_NONE;
+            dst->tail = newlen > 0 ? s_tok[newlen - 1] : STBPE_NONE;
+            __threadfence();
+            dst->ver = m;
+            removed += len - newlen;
+        }
+        __syncthreads();
+    }
+    smem_table_flush<MG>(tab, e);
+    // warp-reduce the match count, one atomic per warp
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) matches += __shfl_down_sync(0xFFFFFFFFu, matches, d);
+    if (lane == 0 && matches) atomicAdd((u64 *)&st->n_matches, (u64)matches);
+    if (tid == 0 && removed) atomicAdd((u64 *)&st->n_live, (u64)(-removed));
+}
+
+// ---------------------------------------------------------------------------------------
+// K4  arg-max: block maxima refresh + reduction with the reference's tie-break
+// ---------------------------------------------------------------------------------------
+__global__ void refresh_kernel(EngineDev e, int all) {
+    const unsigned int n = all ? e.n_blocks : min(e.st->n_dirty, e.n_blocks);
+    const unsigned int lane = threadIdx.x & 31;
+    unsigned int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const unsigned int nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (; w < n; w += nwarps) {
+        const unsigned int blk = all ? w : e.dirty_list[w];
+        const Slot *base = e.table + (u64)blk * STBPE_BLK;
+        u64 bk = STBPE_EMPTY;
+        i64 bc = 0;
+#pragma unroll
+        for (int j = 0; j < STBPE_BLK / 32; ++j) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(base + j * 32 + lane);
+            const u64 k = ((u64)raw.y << 32) | raw.x;
+            const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
+            if (k != STBPE_EMPTY && c > 0 && better(k, c, bk, bc)) {
+                bk = k;
+                bc = c;
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const u64 ok = __shfl_down_sync(0xFFFFFFFFu, bk, d);
+            const i64 oc = __shfl_down_sync(0xFFFFFFFFu, bc, d);
+            if (better(ok, oc, bk, bc)) {
+                bk = ok;
+                bc = oc;
+            }
+        }
+        if (lane == 0) {
+            Slot s;
+            s.key = bk;
+            s.count = bc;
+            e.blockmax[blk] = s;
+            e.dirty_flag[blk] = 0u;
+        }
+    }
+}
+
+__device__ __forceinline__ i64 find_slot(const EngineDev &e, u64 key) {
+    u64 h = mix64(key) & e.mask;
+    for (unsigned int probe = 0; probe < STBPE_MAX_PROBE; ++probe) {
+        const u64 k = *(volatile u64 *)&e.table[h].key;
+        if (k == key) return (i64)h;
+        if (k == STBPE_EMPTY) return -1;
+        h = (h + 1) & e.mask;
+    }
+    return -1;
+}
+
+// Bookkeeping of one selected merge (gpu_tokenizer/bpe_trainer.py:4358-4373): log it, make it
+// current, zero its table entry (no (a,b) pair survives its own merge).
+__device__ __forceinline__ void begin_merge(const EngineDev &e, u64 key, i64 count, int new_id,
+                                            bool may_be_absent) {
+    DevState *st = e.st;
+    const int mnum = st->merges_done;
+    e.merges[2 * mnum] = (int32_t)(key >> 32);
+    e.merges[2 * mnum + 1] = (int32_t)(key & 0xFFFFFFFFull);
+    e.merge_counts[mnum] = count;
+    e.live_before[mnum] = st->n_live;
+    st->cur_a = (int)(key >> 32);
+    st->cur_b = (int)(key & 0xFFFFFFFFull);
+    st->cur_new = new_id;
+    st->cur_count = count;
+    st->merges_done = mnum + 1;
+    const i64 h = find_slot(e, key);
+    if (h >= 0) {
+        e.table[h].count = 0;
+        mark_dirty(e, (u64)h);
+    } else if (!may_be_absent) {
+        atomicOr(&st->error, STBPE_DERR_KEY_MISSING);
+    }
+}
+
+// stop rules of the loop: bpe_trainer.py:4304-4308 (no pairs), :2491-2494 / :4361-4364 (count < 2)
+__device__ __forceinline__ void advance_or_stop(const EngineDev &e, u64 key, i64 count) {
+    DevState *st = e.st;
+    st->n_dirty = 0;
+    if (st->error) {
+        st->stopped = 1;
+        st->stop_reason = 4;
+    } else if (st->merges_done >= st->target) {
+        st->stopped = 1;
+        st->stop_reason = 1;
+    } else if (count <= 0) {
+        st->stopped = 1;
+        st->stop_reason = 2;
+    } else if (count < 2) {
+        st->stopped = 1;
+        st->stop_reason = 3;
+    } else {
+        begin_merge(e, key, count, st->base_vocab + st->merges_done, e.world > 1);
+    }
+}
+
+// mode 0: peek (result into st->peek_*), 1: advance the loop, 2: write candidate to cand[0..1]
+#define STBPE_SELECT_THREADS 256
+__global__ void __launch_bounds__(STBPE_SELECT_THREADS)
+    select_kernel(EngineDev e, int mode, Slot *partial, i64 *cand) {
+    DevState *st = e.st;
+    if (mode == 1 && st->stopped) return;
+    __shared__ u64 s_k[STBPE_SELECT_THREADS / 32];
+    __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
+    __shared__ int s_last;
+    u64 bk = STBPE_EMPTY;
+    i64 bc = 0;
+    for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < e.n_blocks;
+         i += gridDim.x * blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(e.blockmax + i);
+        const u64 k = ((u64)raw.y << 32) | raw.x;
+        const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
+        if (c > 0 && better(k, c, bk, bc)) {
+            bk = k;
+            bc = c;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const u64 ok = __shfl_down_sync(0xFFFFFFFFu, bk, d);
+        const i64 oc = __shfl_down_sync(0xFFFFFFFFu, bc, d);
+        if (better(ok, oc, bk, bc)) {
+            bk = ok;
+            bc = oc;
+        }
+    }
+    if (lane == 0) {
+        s_k[warp] = bk;
+        s_c[warp] = bc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < STBPE_SELECT_THREADS / 32; ++w)
+            if (better(s_k[w], s_c[w], bk, bc)) {
+                bk = s_k[w];
+                bc = s_c[w];
+            }
+        Slot s;
+        s.key = bk;
+        s.count = bc;
+        partial[blockIdx.x] = s;
+        __threadfence();
+        s_last = (atomicAdd(&st->ticket, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last || threadIdx.x != 0) return;
+    __threadfence();
+    bk = STBPE_EMPTY;
+    bc = 0;
+    for (unsigned int i = 0; i < gridDim.x; ++i) {
+        const volatile Slot *p = partial + i;
+        const u64 k = p->key;
+        const i64 c = p->count;
+        if (c > 0 && better(k, c, bk, bc)) {
+            bk = k;
+            bc = c;
+        }
+    }
+    st->ticket = 0;
+    if (mode == 0) {
+        st->peek_key = bk;
+        st->peek_count = bc;
+    } else if (mode == 1) {
+        advance_or_stop(e, bk, bc);
+    } else {
+        cand[0] = (i64)bk;
+        cand[1] = bc;
+    }
+}
+
+// number of keys that hold exactly `count` (tie statistics; full table scan, on demand only)
+__global__ void count_ties_kernel(EngineDev e) {
+    const i64 target = e.st->peek_count;
+    i64 n = 0;
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i <= e.mask; i += (u64)gridDim.x * blockDim.x) {
+        const Slot s = e.table[i];
+        if (s.key != STBPE_EMPTY && s.count == target) ++n;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) n += __shfl_down_sync(0xFFFFFFFFu, n, d);
+    if ((threadIdx.x & 31) == 0 && n) atomicAdd((u64 *)&e.st->peek_ties, (u64)n);
+}
+
+// host-requested merge (stbpe_apply_merge): same bookkeeping as a selected one
+__global__ void force_merge_kernel(EngineDev e, int a, int b, int new_id) {
+    DevState *st = e.st;
+    st->n_dirty = 0;
+    st->stopped = 0;
+    st->stop_reason = 0;
+    st->n_matches = 0;
+    const u64 key = ((u64)(uint32_t)a << 32) | (u64)(uint32_t)b;
+    const i64 h = find_slot(e, key);
+    const i64 count = h >= 0 ? e.table[h].count : 0;
+    begin_merge(e, key, count, new_id, true);  // merging a pair that never occurs is legal
+}
+
+// ---------------------------------------------------------------------------------------
+// exports
+// ---------------------------------------------------------------------------------------
+__global__ void export_table_kernel(EngineDev e, u64 *keys, i64 *counts, i64 cap) {
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i <= e.mask; i += (u64)gridDim.x * blockDim.x) {
+        const Slot s = e.table[i];
+        if (s.key != STBPE_EMPTY && s.count != 0) {
+            const i64 j = (i64)atomicAdd((u64 *)&e.st->export_n, 1ull);
+            if (j < cap) {
+                keys[j] = s.key;
+                counts[j] = s.count;
+            }
+        }
+    }
+}
+
+// tile_off[t] = exclusive prefix of the current tile lengths (computed by the host)
+__global__ void export_stream_kernel(EngineDev e, const i64 *__restrict__ tile_off, int32_t *out) {
+    for (int tile = blockIdx.x; tile < e.n_tiles; tile += gridDim.x) {
+        const int len = (int)(tile_off[tile + 1] - tile_off[tile]);
+        const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
+        for (int i = threadIdx.x; i < len; i += blockDim.x) out[tile_off[tile] + i] = (int32_t)g[i];
+    }
+}
+
+__global__ void tile_lens_kernel(EngineDev e, i64 *lens) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= e.n_tiles) return;
+    TileRec r;
+    current_rec(e, t, 0x7FFFFFFF, r);
+    lens[t] = r.len;
+}
+
+// ---------------------------------------------------------------------------------------
+// multi-GPU: drain the rank-local delta table into per-owner outbox chunks; apply an inbox
+// ---------------------------------------------------------------------------------------
+__global__ void outbox_reset_kernel(EngineDev e) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < e.world) {
+        Slot h;
+        h.key = 0;
+        h.count = 0;
+        e.outbox[(i64)p * (e.cap_per_peer + 1)] = h;
+    }
+}
+
+__global__ void drain_ltable_kernel(EngineDev e) {
+    const unsigned int n = e.st->n_ltouched;
+    for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        Slot *s = &e.ltable[e.ltouched[i]];
+        const Slot v = *s;
+        s->key = STBPE_EMPTY;
+        s->count = 0;
+        if (v.count == 0) continue;
+        const int owner = owner_of(v.key, e.world);
+        Slot *chunk = e.outbox + (i64)owner * (e.cap_per_peer + 1);
+        const i64 j = (i64)atomicAdd(&chunk[0].key, 1ull);
+        if (j < e.cap_per_peer)
+            chunk[1 + j] = v;
+        else
+            atomicOr(&e.st->error, STBPE_DERR_OUTBOX_FULL);
+    }
+}
+
+__global__ void ltouched_reset_kernel(EngineDev e) { e.st->n_ltouched = 0; }
+
+__global__ void apply_inbox_kernel(EngineDev e) {
+    for (int p = 0; p < e.world; ++p) {
+        const Slot *chunk = e.inbox + (i64)p * (e.cap_per_peer + 1);
+        i64 n = (i64)chunk[0].key;
+        if (n > e.cap_per_peer) n = e.cap_per_peer;
+        for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) {
+            const Slot v = chunk[1 + i];
+            table_add(e, v.key, v.count);
+        }
+    }
+}
+
+// every rank evaluates the same candidates and reaches the same decision
+__global__ void commit_kernel(EngineDev e, const i64 *all_cands) {
+    DevState *st = e.st;
+    if (st->stopped) return;
+    u64 bk = STBPE_EMPTY;
+    i64 bc = 0;
+    for (int r = 0; r < e.world; ++r) {
+        const u64 k = (u64)all_cands[2 * r];
+        const i64 c = all_cands[2 * r + 1];
+        if (c > 0 && better(k, c, bk, bc)) {
+            bk = k;
+            bc = c;
+        }
+    }
+    advance_or_stop(e, bk, bc);
+}
