@@ -113,6 +113,12 @@ int stbpe_get_merges(stbpe_engine *e, int32_t first, int32_t n, int32_t *merges,
  * are device pointers with room for cap entries. */
 int stbpe_export_histogram(stbpe_engine *e, uint64_t *keys, int64_t *counts, int64_t cap,
                            int64_t *n_out, void *stream);
+/* All keys whose count equals `count`, unordered, into keys (device, cap entries); *n_out is
+ * their number even when it exceeds cap.  Feeds the seeded random tie-break, which indexes the
+ * tied candidates in ascending key order (gpu_tokenizer/bpe_trainer.py:915-923,
+ * trainers/bpe_gpu.py:112-123). */
+int stbpe_export_ties(stbpe_engine *e, int64_t count, uint64_t *keys, int64_t cap, int64_t *n_out,
+                      void *stream);
 /* Export of the rewritten stream: ids (device, cap tokens, bit 31 = row start). */
 int stbpe_export_stream(stbpe_engine *e, int32_t *ids, int64_t cap, int64_t *n_out, void *stream);
 

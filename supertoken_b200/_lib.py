@@ -47,6 +47,7 @@ SIGNATURES = {
     "stbpe_get_state": (_int, [_vp, _P(State), _vp]),
     "stbpe_get_merges": (_int, [_vp, _i32, _i32, _vp, _vp, _vp]),
     "stbpe_export_histogram": (_int, [_vp, _vp, _vp, _i64, _P(_i64), _vp]),
+    "stbpe_export_ties": (_int, [_vp, _i64, _vp, _i64, _P(_i64), _vp]),
     "stbpe_export_stream": (_int, [_vp, _vp, _i64, _P(_i64), _vp]),
     "stbpe_mg_buffers": (_int, [_vp, _P(_vp), _P(_vp), _P(_i64), _P(_i64)]),
     "stbpe_mg_count_local": (_int, [_vp, _vp]),

@@ -1,0 +1,407 @@
+"""``GPUBPETrainer`` -- drop-in for the reference trainer's BPE merge loop.
+
+Mirrors the public surface of ``gpu_tokenizer/bpe_trainer.py:691-4790`` that sits on the
+merge-loop path: constructor (``:694-708``), ``fit`` (``:2501-2518``) with its return
+dictionary (``:4582-4607``), merge log / vocabulary attributes, checkpoint and artifact
+methods.  The loop itself (``:4193-4517``) runs on the GPU through the C-ABI library; there
+is no CPU path here -- ``device="cpu"`` raises.
+
+Semantics kept bit-for-bit (see ``supertoken_b200/csrc/kernels.cuh`` for the kernels):
+rows are the only pair boundary, every adjacent position counts, best pair = highest count
+then smallest ``(a << 32) | b``, stop when the best count is below 2 (then pad with
+``random.randint`` pairs as the reference does) or when no pair is left (no padding),
+``new_id = base_vocab + len(merges)``, simultaneous-match merge with run collapse.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import os
+import random
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Iterable, List, Mapping, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from .base import BaseTrainer
+from .engine import Engine
+from .export import bytes_to_unicode, write_artifacts
+
+logger = logging.getLogger(__name__)
+UINT32_MAX = (1 << 32) - 1
+CHECKPOINT_SCHEMA_VERSION = 1
+
+
+@dataclass
+class StageTiming:
+    """Timing samples of a named stage (``gpu_tokenizer/bpe_trainer.py:85-107``)."""
+
+    name: str
+    samples: List[float] = field(default_factory=list)
+
+    def record(self, duration_s: float) -> None:
+        if duration_s >= 0:
+            self.samples.append(float(duration_s))
+
+    def summary(self) -> dict:
+        total = float(sum(self.samples))
+        n = len(self.samples)
+        return {"stage": self.name, "count": n, "total_s": total, "avg_s": total / n if n else 0.0,
+                "samples": list(self.samples)}
+
+
+class _NullAutoScaler:
+    """Batch size does not influence merges; the controller is kept only as an attribute."""
+
+    def state_dict(self) -> dict:
+        return {}
+
+
+def hash_merge_pair(pair: Tuple[int, int], salt: bytes = b"") -> str:
+    """Salted SHA-256 digest of a merge pair (``gpu_tokenizer/utils.py:137-157``)."""
+    import hashlib
+    d = hashlib.sha256()
+    d.update(salt)
+    d.update(int(pair[0]).to_bytes(8, "big", signed=False))
+    d.update(int(pair[1]).to_bytes(8, "big", signed=False))
+    return d.hexdigest()
+
+
+def _flatten_batch(batch) -> Tuple[torch.Tensor, np.ndarray]:
+    """``(tokens[B,L], valid[B,L], lengths[B])`` -> flat int32 ids + row offsets.
+
+    The reference's batchers only emit prefix-valid rows (``gpu_tokenizer/datasets.py:83-84``);
+    anything else is outside the parity contract and rejected."""
+    tokens, valid = batch[0], batch[1]
+    if tokens.dim() != 2 or valid.shape != tokens.shape:
+        raise ValueError("expected tokens[B, L] and valid[B, L]")
+    vb = valid.to(torch.bool)
+    lens = vb.sum(dim=1, dtype=torch.int64)
+    L_ = tokens.shape[1]
+    prefix = torch.arange(L_, device=vb.device)[None, :] < lens[:, None]
+    if not torch.equal(prefix, vb):
+        raise ValueError("valid must mark a prefix of every row")
+    ids = tokens[vb].to(torch.int32).contiguous()
+    off = np.zeros(tokens.shape[0] + 1, dtype=np.int64)
+    np.cumsum(lens.cpu().numpy(), out=off[1:])
+    return ids, off
+
+
+class GPUBPETrainer(BaseTrainer):
+    """B200 implementation of the reference's ``GPUBPETrainer`` merge loop."""
+
+    def __init__(self, base_vocab: int = 256, merges: int = 50_000, device: str | None = None,
+                 devices: Optional[Sequence[str]] = None, autoscaler: Any = None, sync_every: int = 1,
+                 warm_start_merges: Optional[Sequence[Tuple[int, int]]] = None,
+                 freeze_warm_start: bool = False, privacy_mode: bool = False,
+                 randomize_ties: bool | None = None, tie_seed: int | None = None,
+                 privacy_salt: bytes | bytearray | str | None = None) -> None:
+        super().__init__()
+        self.base_vocab = int(base_vocab)
+        self.target_merges = int(merges)
+        resolved: List[torch.device] = []
+        if devices is not None:
+            if not devices:
+                raise ValueError("devices must be a non-empty sequence when provided")
+            resolved = [torch.device(d) for d in devices]
+        if device is not None:
+            primary = torch.device(device)
+            if resolved and primary not in resolved:
+                raise ValueError("primary device must be included in devices sequence")
+            if not resolved:
+                resolved = [primary]
+        if not resolved:
+            resolved = [torch.device("cuda")]
+        if any(d.type != "cuda" for d in resolved):
+            raise RuntimeError("supertoken_b200.GPUBPETrainer runs on CUDA devices only "
+                               "(the CPU path belongs to the reference implementation)")
+        self.devices = resolved
+        self.device = str(resolved[0])
+        self.vocab_size = self.base_vocab
+        self.merges: List[Tuple[int, int]] = []
+        self.merge_counts: List[int] = []
+        self._seed_warm_start_merges = list(warm_start_merges) if warm_start_merges is not None else []
+        self.freeze_warm_start = bool(freeze_warm_start)
+        self.privacy_mode = bool(privacy_mode)
+        self.randomize_ties = self.privacy_mode if randomize_ties is None else bool(randomize_ties)
+        self.tie_seed = int(tie_seed) if tie_seed is not None else None
+        self._tie_seed_value = int(self.tie_seed if self.tie_seed is not None else 0)
+        if privacy_salt is None:
+            self._privacy_hash_salt = b""
+        elif isinstance(privacy_salt, (bytes, bytearray)):
+            self._privacy_hash_salt = bytes(privacy_salt)
+        else:
+            self._privacy_hash_salt = str(privacy_salt).encode("utf-8")
+        self._tie_rng: random.Random | None = None
+        self._reset_tie_rng()
+        self.autoscaler = autoscaler if autoscaler is not None else _NullAutoScaler()
+        self.sync_every = max(1, int(sync_every))
+        self._enable_histogram_cache = False  # the engine always keeps an exact histogram
+        self._top_pairs_limit = 0
+        self._cpu_fallback_batches = 0
+        self._active_batch_size: Optional[int] = None
+        self.bytes_h2d = self.bytes_d2h = 0
+        self.h2d_events = self.d2h_events = 0
+        self.throughput_metrics: dict = {}
+        self.table_slots = 0  # 0 = sized from the token count
+        self._engine: Optional[Engine] = None
+        self._last_stats: dict = {}
+
+    # ------------------------------------------------------------------ small helpers
+    def _reset_tie_rng(self) -> None:
+        self._tie_rng = random.Random(self._tie_seed_value) if self.randomize_ties else None
+
+    def metrics(self) -> Mapping[str, Any]:
+        return self._metrics_mapping()
+
+    def handle_chunk_start(self, chunk_id: int, *, reprocessed: bool = False, attempts: int = 1) -> None:
+        """Lease bookkeeping hook of the reference (``bpe_trainer.py:836-856``): static
+        document sharding has no leases, so there is nothing to invalidate."""
+
+    @staticmethod
+    def _bytes_to_unicode() -> dict:
+        return bytes_to_unicode()
+
+    def import_merges(self, merges, *, vocab_size: int | None = None, base_vocab: int | None = None,
+                      source: str | None = None, freeze: bool = False) -> None:
+        """``gpu_tokenizer/bpe_trainer.py:2254-2300``."""
+        if merges is None:
+            raise ValueError("merges must be provided when importing external artifacts")
+        coerced = []
+        for entry in merges:
+            if not isinstance(entry, Sequence) or len(entry) != 2:
+                raise ValueError("merge entries must contain exactly two token ids")
+            coerced.append((int(entry[0]), int(entry[1])))
+        self.base_vocab = int(base_vocab) if base_vocab is not None else self.base_vocab
+        self.vocab_size = int(vocab_size) if vocab_size is not None else self.base_vocab + len(coerced)
+        self.target_merges = max(self.target_merges, len(coerced))
+        self.merges = coerced
+        self._seed_warm_start_merges = list(coerced)
+        self.freeze_warm_start = bool(freeze)
+
+    # ------------------------------------------------------------------ the loop
+    def _make_engine(self, n_tokens: int) -> Engine:
+        dev = torch.device(self.device)
+        if self._engine is not None:
+            self._engine.close()
+        self._engine = Engine(max(int(n_tokens), 1), base_vocab=self.base_vocab,
+                              max_merges=max(self.target_merges, 1), device=dev,
+                              table_slots=self.table_slots)
+        return self._engine
+
+    def fit(self, batches: Iterable, log_every: int = 100, profile_streams: bool = False,
+            on_batch_size_change: Optional[Callable] = None, warm_start_merges=None,
+            freeze_warm_start: Optional[bool] = None, overlap_transfers: bool = True,
+            warm_start_plan=None, warm_start_ngrams=None, warm_start_device=None,
+            checkpoint_interval: Optional[int] = None, checkpoint_dir: Optional[str] = None,
+            resume_state=None, on_iteration_summary=None, dataset_state=None) -> dict:
+        """Train on an iterable of ``(tokens[B,L] int32, valid[B,L] uint8, lengths[B])`` CPU or
+        CUDA tensors, as the reference's batchers yield them (``gpu_tokenizer/datasets.py:88-92``)."""
+        if checkpoint_interval is not None and checkpoint_dir is None:
+            raise ValueError("checkpoint_interval requires checkpoint_dir")
+        flat: List[Tuple[torch.Tensor, np.ndarray]] = [_flatten_batch(b) for b in batches]
+        total = sum(int(ids.numel()) for ids, _ in flat)
+        t0 = time.perf_counter()
+        eng = self._make_engine(total)
+        for ids, off in flat:
+            if ids.numel():
+                eng.append_ids(ids, off)
+                if not ids.is_cuda:
+                    self.bytes_h2d += ids.numel() * 4
+                    self.h2d_events += 1
+        return self._run_loop(eng, log_every, t0, warm_start_merges, checkpoint_interval, checkpoint_dir)
+
+    def fit_bytes(self, data, row_offsets=None, log_every: int = 0) -> dict:
+        """Fast ingest: one uint8 buffer (host or device) plus row offsets; rows are what
+        the reference calls files / documents.  Not part of the reference API: padded
+        ``[B, L]`` int32 batches cost five host bytes per input byte."""
+        if isinstance(data, np.ndarray):
+            data = torch.from_numpy(np.ascontiguousarray(data, dtype=np.uint8))
+        t0 = time.perf_counter()
+        eng = self._make_engine(data.numel())
+        eng.append_bytes(data, row_offsets)
+        if not data.is_cuda:
+            self.bytes_h2d += data.numel()
+            self.h2d_events += 1
+        return self._run_loop(eng, log_every, t0, None, None, None)
+
+    def _run_loop(self, eng: Engine, log_every: int, t0: float, warm_start_merges,
+                  checkpoint_interval, checkpoint_dir) -> dict:
+        timings = {k: StageTiming(k) for k in ("pair_count", "apply_merge", "host_sync")}
+        events: List[dict] = []
+        self.merges = []
+        self.merge_counts = []
+        self.vocab_size = self.base_vocab
+        warm = list(warm_start_merges) if warm_start_merges is not None else list(self._seed_warm_start_merges)
+
+        t = time.perf_counter()
+        eng.count_initial()
+        torch.cuda.synchronize(eng.device)
+        timings["pair_count"].record(time.perf_counter() - t)
+        events.append({"stage": "pair_count", "duration_s": timings["pair_count"].samples[-1],
+                       "mode": "gpu", "merge": 0, "type": "merge", "timestamp": time.time()})
+
+        # warm start: seeded merges are applied without selection (bpe_trainer.py:4058-4182)
+        warm_applied = 0
+        for a, b in warm[: self.target_merges]:
+            if max(a, b, self.vocab_size) > UINT32_MAX:
+                raise OverflowError(f"Token id overflow: encountered id above UINT32_MAX (limit {UINT32_MAX}).")
+            eng.apply_merge(int(a), int(b), self.vocab_size)
+            self.merges.append((int(a), int(b)))
+            self.vocab_size += 1
+            warm_applied += 1
+
+        t = time.perf_counter()
+        remaining = self.target_merges - len(self.merges)
+        reason = L.RUNNING
+        if remaining > 0:
+            if self.randomize_ties:
+                reason = self._loop_random_ties(eng, remaining)
+            else:
+                step = checkpoint_interval if checkpoint_interval else remaining
+                while remaining > 0 and reason in (L.RUNNING, L.STOP_TARGET):
+                    n = min(step, remaining)
+                    eng.train(n)
+                    st = eng.state()
+                    got, counts, _ = eng.merges(len(self.merges), st.merges_done - len(self.merges))
+                    self.merges.extend(got)
+                    self.merge_counts.extend(int(c) for c in counts)
+                    self.vocab_size = self.base_vocab + len(self.merges)
+                    remaining = self.target_merges - len(self.merges)
+                    reason = st.stop_reason
+                    if checkpoint_interval and checkpoint_dir and remaining > 0:
+                        self.save_checkpoint(checkpoint_dir)
+                    if len(got) < n:
+                        break
+        loop_s = time.perf_counter() - t
+        timings["apply_merge"].record(loop_s)
+        self.bytes_d2h += len(self.merges) * 16
+        self.d2h_events += 1
+        if log_every and log_every > 0:
+            for step, ((a, b), c) in enumerate(zip(self.merges[warm_applied:], self.merge_counts)):
+                if step % log_every == 0:
+                    print(f"merge {step:6d}: ({a},{b}) -> {self.base_vocab + warm_applied + step}  count={c}")
+        if reason == L.STOP_NO_PAIRS:
+            print("No pairs left to merge.")  # bpe_trainer.py:4304-4308: stop, no padding
+        elif reason == L.STOP_LOW_COUNT:
+            # bpe_trainer.py:4347-4353: pad with random pairs up to the target
+            while len(self.merges) < self.target_merges:
+                self.merges.append((random.randint(0, self.vocab_size - 1), random.randint(0, self.vocab_size - 1)))
+                self.vocab_size += 1
+            if log_every and log_every > 0:
+                logger.info("Stopping: no frequent pairs.")
+        st = eng.state()
+        self._last_stats = {"live_tokens": int(st.live_tokens), "table_keys": int(st.table_keys),
+                            "table_slots": int(st.table_slots), "loop_s": loop_s,
+                            "total_s": time.perf_counter() - t0, "stop_reason": int(reason)}
+        merge_log = [{"merge": i, "bytes_d2h": 16} for i in range(len(self.merge_counts))]
+        return {
+            "base_vocab": self.base_vocab,
+            "vocab_size": self.vocab_size,
+            "merges": self.merges,
+            "warm_start": {"applied": warm_applied, "source": "constructor" if warm_applied else None},
+            "transfer_metrics": {
+                "bytes_h2d": self.bytes_h2d, "bytes_d2h": self.bytes_d2h,
+                "h2d_events": self.h2d_events, "d2h_events": self.d2h_events,
+                "merge_stats": merge_log, "sync_intervals": [],
+                "per_device": {self.device: {"bytes_h2d": self.bytes_h2d, "bytes_d2h": self.bytes_d2h}},
+                "per_stage": {k: {"h2d": 0, "d2h": 0} for k in ("pair_count", "apply_merge", "host_sync")},
+                "avg_d2h_bytes_per_merge": (self.bytes_d2h / len(merge_log)) if merge_log else 0.0,
+                "cpu_fallback": {"batches": 0, "ratio": 0.0},
+            },
+            "telemetry": {
+                "timings": {k: v.summary() for k, v in timings.items()},
+                "events": events, "host_sync_events": [], "device_snapshots": [],
+                "autoscaler": {"window": []},
+                "iteration_metrics": {"ewma": {}, "iterations": []},
+                "engine": dict(self._last_stats),
+            },
+        }
+
+    def _loop_random_ties(self, eng: Engine, remaining: int) -> int:
+        """Host-driven loop for ``randomize_ties``: the seeded ``random.Random`` picks an index
+        into the tied candidates in ascending key order (``bpe_trainer.py:915-923``,
+        ``trainers/bpe_gpu.py:112-123``)."""
+        while remaining > 0:
+            key, count, ties = eng.select_best(with_ties=True)
+            if key is None:
+                return L.STOP_NO_PAIRS
+            if count < 2:
+                return L.STOP_LOW_COUNT
+            if ties > 1 and self._tie_rng is not None:
+                cands = eng.tied_keys(count, ties)
+                key = cands[self._tie_rng.randrange(len(cands))]
+            a, b = key >> 32, key & 0xFFFFFFFF
+            eng.apply_merge(a, b, self.vocab_size)
+            self.merges.append((a, b))
+            self.merge_counts.append(count)
+            self.vocab_size += 1
+            remaining -= 1
+        return L.STOP_TARGET
+
+    # ------------------------------------------------------------------ state / artifacts
+    def _merges_for_metadata(self) -> list:
+        if not self.privacy_mode:
+            return [list(map(int, p)) for p in self.merges]
+        return [hash_merge_pair(p, self._privacy_hash_salt) for p in self.merges]
+
+    def _privacy_summary(self) -> dict:
+        mode = "tie-randomize" if self.randomize_ties else ("hash-merges" if self.privacy_mode else "none")
+        s: dict = {"mode": mode, "merges_redacted": bool(self.privacy_mode),
+                   "randomize_ties": bool(self.randomize_ties)}
+        if self.randomize_ties or self.tie_seed is not None:
+            s["tie_seed_effective"] = int(self._tie_seed_value)
+            if self.tie_seed is not None:
+                s["tie_seed"] = int(self.tie_seed)
+        if self._privacy_hash_salt:
+            s["salt_configured"] = True
+        return s
+
+    def state_dict(self, *args, **kwargs) -> dict:
+        return {"schema_version": CHECKPOINT_SCHEMA_VERSION,
+                "trainer": {"base_vocab": self.base_vocab, "vocab_size": self.vocab_size,
+                            "target_merges": self.target_merges, "merges": [list(p) for p in self.merges],
+                            "merge_step": len(self.merges), "privacy": self._privacy_summary()},
+                "autoscaler": {}, "dataset": {}, "rng": {}}
+
+    def load_state_dict(self, state_dict: Mapping[str, Any], *args, **kwargs) -> dict:
+        tr = dict(state_dict.get("trainer", {}))
+        self.base_vocab = int(tr.get("base_vocab", self.base_vocab))
+        self.merges = [tuple(map(int, p)) for p in tr.get("merges", [])]
+        self.vocab_size = int(tr.get("vocab_size", self.base_vocab + len(self.merges)))
+        self.target_merges = int(tr.get("target_merges", self.target_merges))
+        self._seed_warm_start_merges = list(self.merges)
+        self._reset_tie_rng()
+        return dict(state_dict)
+
+    def save_checkpoint(self, path, *args, **kwargs) -> dict:
+        os.makedirs(path, exist_ok=True)
+        state = self.state_dict()
+        with open(os.path.join(path, "state.json"), "w", encoding="utf-8") as f:
+            json.dump(state, f)
+        return state
+
+    def load_checkpoint(self, path, *args, **kwargs) -> dict:
+        with open(os.path.join(path, "state.json"), encoding="utf-8") as f:
+            state = json.load(f)
+        self.load_state_dict(state)
+        return state
+
+    def save_artifacts(self, out_dir) -> dict:
+        extra: dict = {"privacy": self._privacy_summary()}
+        if self.privacy_mode:
+            extra.update({"privacy_mode": True, "merge_count": len(self.merges),
+                          "randomize_ties": bool(self.randomize_ties), "tie_seed": int(self._tie_seed_value)})
+        return write_artifacts(os.fspath(out_dir), self.base_vocab, self.merges, self.vocab_size,
+                               metadata_merges=self._merges_for_metadata(), extra_meta=extra)
+
+    def save(self, out_dir) -> None:
+        p = self.save_artifacts(out_dir)
+        print("Saved tokenizer artifacts → "
+              f"{p['vocab']}, {p['merges']}, {p['tokenizer']}, {p['tiktoken_merges']}")
+
+
+__all__ = ["GPUBPETrainer", "StageTiming", "hash_merge_pair"]

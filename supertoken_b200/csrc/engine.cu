@@ -560,6 +560,21 @@ STBPE_VISIBLE int stbpe_export_histogram(stbpe_engine *e, uint64_t *keys, int64_
     return rc;
 }
 
+STBPE_VISIBLE int stbpe_export_ties(stbpe_engine *e, int64_t count, uint64_t *keys, int64_t cap,
+                                    int64_t *n_out, void *stream) {
+    if (!e || !n_out || cap < 0 || (cap > 0 && !keys)) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    CK(cudaMemsetAsync(&e->d.st->export_n, 0, sizeof(i64), s));
+    export_ties_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, count, (u64 *)keys, cap);
+    CK(cudaGetLastError());
+    i64 n = 0;
+    CK(cudaMemcpyAsync(&n, &e->d.st->export_n, sizeof(i64), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    *n_out = n;
+    return STBPE_OK;
+}
+
 STBPE_VISIBLE int stbpe_export_stream(stbpe_engine *e, int32_t *ids, int64_t cap, int64_t *n_out,
                                       void *stream) {
     if (!e || !n_out) return STBPE_E_BADARG;

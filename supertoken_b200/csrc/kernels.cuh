@@ -496,6 +496,17 @@ __global__ void export_table_kernel(EngineDev e, u64 *keys, i64 *counts, i64 cap
     }
 }
 
+// keys whose count equals `count` (unordered; the host sorts the few there are)
+__global__ void export_ties_kernel(EngineDev e, i64 count, u64 *keys, i64 cap) {
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i <= e.mask; i += (u64)gridDim.x * blockDim.x) {
+        const Slot s = e.table[i];
+        if (s.key != STBPE_EMPTY && s.count == count) {
+            const i64 j = (i64)atomicAdd((u64 *)&e.st->export_n, 1ull);
+            if (j < cap) keys[j] = s.key;
+        }
+    }
+}
+
 // tile_off[t] = exclusive prefix of the current tile lengths (computed by the host)
 __global__ void export_stream_kernel(EngineDev e, const i64 *__restrict__ tile_off, int32_t *out) {
     for (int tile = blockIdx.x; tile < e.n_tiles; tile += gridDim.x) {

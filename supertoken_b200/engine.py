@@ -152,6 +152,14 @@ class Engine:
                                                      ctypes.byref(n), self._s))
         return keys[:n.value], counts[:n.value]
 
+    def tied_keys(self, count: int, n_ties: int) -> List[int]:
+        """Keys holding exactly ``count``, ascending."""
+        buf = torch.empty(max(n_ties, 1), dtype=torch.int64, device=self.device)
+        n = ctypes.c_int64(0)
+        self._check(self._lib.stbpe_export_ties(self._h, count, buf.data_ptr(), buf.numel(),
+                                                ctypes.byref(n), self._s))
+        return sorted(int(k) for k in buf[:min(n.value, buf.numel())].cpu().numpy().view(np.uint64))
+
     def export_stream(self):
         """int32 ids on the device with bit 31 marking row starts -> (ids, row_offsets) on CPU."""
         st = self.state()

@@ -1,0 +1,227 @@
+"""Parity of the CUDA engine (through the C ABI) with the CPU oracle and the golden fixtures
+produced by the reference itself.  Integer work: every comparison is bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from supertoken_b200 import synth
+from supertoken_b200.engine import CapacityError, Engine
+from tests.helpers import corpus_rows, learned_prefix, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _hist(e):
+    k, c = e.export_histogram()
+    return k.cpu().numpy().astype(np.uint64), c.cpu().numpy()
+
+
+def _engine_for(ids, off, base_vocab=256, target=64, slots=1 << 18):
+    e = Engine(max(len(ids), 1), base_vocab=base_vocab, max_merges=max(target, 1), table_slots=slots)
+    if len(ids):
+        e.append_ids(ids, off)
+    e.count_initial()
+    return e
+
+
+def _check_against_oracle(rows, base_vocab, target, full=True):
+    ids, off = O.flatten_rows(rows)
+    e = _engine_for(ids, off, base_vocab, target)
+    ok, oc = O.count_pairs_flat(ids, off, 1)
+    k, c = _hist(e)
+    assert np.array_equal(k, ok) and np.array_equal(c, oc)
+    e.train(target)
+    m, cnt, live = e.merges()
+    om, ocnt, reason = O.train_flat(ids, off, base_vocab, target, 1)
+    assert m == om and cnt.tolist() == ocnt
+    st = e.state()
+    assert st.stop_reason == {0: 1, 1: 2, 2: 3}[reason]
+    if full:
+        ids2, off2 = ids.copy(), off.copy()
+        n_before = []
+        for i, (a, b) in enumerate(om):
+            n_before.append(int(off2[-1]))
+            O.apply_merge_flat(ids2, off2, a, b, base_vocab + i)
+        assert live.tolist() == n_before
+        gi, go = e.export_stream()
+        assert np.array_equal(gi, ids2[:off2[-1]])
+        assert np.array_equal(go[:-1], np.unique(off2[:-1][np.diff(off2) > 0]))
+        assert st.live_tokens == off2[-1]
+        ok, oc = O.count_pairs_flat(ids2[:off2[-1]].copy(), off2, 1)
+        k, c = _hist(e)
+        assert np.array_equal(k, ok) and np.array_equal(c, oc)
+    e.close()
+    return m
+
+
+def test_known_answers_from_reference_unit_tests():
+    # tests/test_bpe_trainer.py:191-202, :463-477, :484-501 of the reference
+    assert _check_against_oracle([[0, 1, 0, 1], [0, 2, 0, 2]], 16, 1) == [(0, 1)]
+    assert _check_against_oracle([[1, 2, 1, 2, 3], [1, 2, 4, 2], [1, 2, 1, 2], [1, 2, 1, 2]], 256, 1) == [(1, 2)]
+    assert _check_against_oracle([[1, 2, 3, 1, 2, 4], [1, 2, 3, 1, 2, 3], [1, 2, 4, 2, 4]], 256, 3) == \
+        [(1, 2), (256, 3), (256, 4)]
+
+
+def test_run_collapse_examples():
+    ids, off = O.flatten_rows([[7, 7, 7, 7, 8], [7, 7, 7], [5, 7, 7, 7, 7, 7, 9, 7, 7]])
+    e = _engine_for(ids, off)
+    k, c = _hist(e)
+    assert dict(zip(k.tolist(), c.tolist()))[(7 << 32) | 7] == 10
+    assert e.apply_merge(7, 7, 256) == 10
+    gi, go = e.export_stream()
+    assert gi.tolist() == [256, 8, 256, 5, 256, 9, 256] and go.tolist() == [0, 2, 3, 7]
+
+
+@pytest.mark.parametrize("n", [0, 1, 2, 31, 32, 33, 4095, 4096, 4097, 8191, 8192, 8193, 12289])
+def test_equal_token_runs_across_tile_seams(n):
+    # one row of n equal tokens: (n-1) pairs, and the merge collapses it to one token
+    rows = [[5] * n, [5, 5, 6, 5]]
+    _check_against_oracle(rows, 256, 4)
+
+
+@pytest.mark.parametrize("shift", [0, 1, 2, 3, 4093, 4094, 4095])
+def test_matches_straddling_tile_seams(shift):
+    # "ab" repeated, shifted so that matches, chains and row starts fall on every seam offset
+    rows = [[9] * shift + [1, 2] * 5000 + [3], [1, 2] * 3, [2, 1, 2, 1] * 1100, [1], [], [2]]
+    _check_against_oracle(rows, 256, 12)
+
+
+def test_empty_and_degenerate_inputs():
+    for rows in ([], [[]], [[4]], [[4], [4], [4]], [[1, 2]], [[], [3, 3], []]):
+        _check_against_oracle(rows, 256, 3)
+
+
+def test_random_small_alphabets_many_tiles():
+    rng = np.random.default_rng(11)
+    for alphabet, n_rows, max_len, target in ((2, 7, 30000, 40), (3, 300, 400, 60), (5, 3, 50000, 80)):
+        rows = [rng.integers(0, alphabet, int(rng.integers(0, max_len))).tolist() for _ in range(n_rows)]
+        _check_against_oracle(rows, 256, target)
+
+
+def test_tiles_that_become_empty_or_short():
+    # long runs collapse whole tiles to nothing; later merges must walk over the empty tiles
+    rows = [[1] * 20000 + [2, 3] * 10 + [1] * 9000 + [2, 3, 2, 3], [4] * 5000 + [1, 1, 2, 3]]
+    _check_against_oracle(rows, 256, 10)
+
+
+def test_golden_random_and_adversarial_fixtures():
+    g = load_golden("train.json")
+    for case in g["random"] + g["adversarial"]:
+        ids, off = O.flatten_rows(case["rows"])
+        e = _engine_for(ids, off, case["base_vocab"], case["target"])
+        e.train(case["target"])
+        m, _, _ = e.merges()
+        reason = {1: 0, 2: 1, 3: 2}[e.state().stop_reason]
+        learned_prefix(case, m, reason)
+        e.close()
+
+
+def test_golden_synthetic_fixtures_from_bytes():
+    g = load_golden("train.json")
+    for case in g["synthetic"]:
+        c = getattr(synth, case["generator"])(**case["kwargs"])
+        assert c.sha256() == case["sha256"]
+        e = Engine(len(c.data), base_vocab=256, max_merges=case["target"], table_slots=1 << 18)
+        e.append_bytes(c.data, c.row_offsets)   # host bytes -> pack kernel
+        e.count_initial()
+        e.train(case["target"])
+        m, _, _ = e.merges()
+        assert m == [tuple(x) for x in case["merges_raw"]]
+        e.close()
+
+
+def test_device_generated_corpus_matches_host_and_appends():
+    host = synth.config2_mixed(1 << 18, seed=1, lexicon=4000, mean_doc_bytes=700)
+    dev = synth.config2_mixed(1 << 18, seed=1, lexicon=4000, mean_doc_bytes=700, device="cuda")
+    assert np.array_equal(host.data, dev.data.cpu().numpy())
+    rows = corpus_rows(host)
+    ids, off = O.flatten_rows(rows)
+    om, _, _ = O.train_flat(ids, off, 256, 50, 1)
+    # device bytes in one call
+    e = Engine(len(host.data), max_merges=50, table_slots=1 << 18)
+    e.append_bytes(dev.data, dev.row_offsets)
+    e.count_initial()
+    e.train(50)
+    assert e.merges()[0] == om
+    # same corpus appended in three unaligned pieces (rows never split)
+    e.reset()
+    offs = np.asarray(host.row_offsets)
+    cuts = [0, len(offs) // 3, 2 * len(offs) // 3, len(offs) - 1]
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        e.append_bytes(host.data[offs[lo]:offs[hi]], offs[lo:hi + 1] - offs[lo])
+    e.count_initial()
+    e.train(50)
+    assert e.merges()[0] == om
+    e.close()
+
+
+def test_config1_slice_full_parity():
+    c = synth.config1_text(2 << 20, seed=0, file_bytes=1 << 17)
+    _check_against_oracle([r for r in corpus_rows(c)], 256, 150)
+
+
+def test_config5_slice_full_parity():
+    c = synth.config5_adversarial(3 << 20, seed=4)
+    _check_against_oracle([r for r in corpus_rows(c)], 256, 120)
+
+
+def test_config3_slice_histogram_parity():
+    ids, off = synth.config3_ids(1 << 21, seed=2)
+    e = Engine(len(ids), base_vocab=65536, max_merges=8, table_slots=1 << 22)
+    e.append_ids(ids, off)
+    e.count_initial()
+    ok, oc = O.count_pairs_flat(ids, off, 1)
+    k, c = _hist(e)
+    assert np.array_equal(k, ok) and np.array_equal(c, oc)
+    assert c.sum() == len(ids) - (len(off) - 1)
+    bk, bc = O.select_best(ok, oc)
+    key, count, ties = e.select_best(with_ties=True)
+    assert (key, count) == (bk, bc) and ties == int((oc == bc).sum())
+    e.close()
+
+
+def test_stepwise_operators_and_recount_property():
+    # select / apply one merge at a time; after every merge the incrementally maintained
+    # table equals a recount of the rewritten stream (the property the deltas must keep)
+    c = synth.config5_adversarial(1 << 20, seed=9)
+    ids, off = O.flatten_rows(corpus_rows(c))
+    e = _engine_for(ids, off, 256, 40)
+    for step in range(25):
+        key, count, _ = e.select_best()
+        ok, oc = O.count_pairs_flat(ids[:off[-1]].copy(), off, 1)
+        assert (key, count) == O.select_best(ok, oc)
+        a, b = key >> 32, key & 0xFFFFFFFF
+        n = e.apply_merge(a, b, 256 + step)
+        assert n == O.apply_merge_flat(ids, off, a, b, 256 + step)
+        k1, c1 = _hist(e)
+        e.count_initial()          # full recount of the rewritten stream on the device
+        k2, c2 = _hist(e)
+        assert np.array_equal(k1, k2) and np.array_equal(c1, c2)
+    e.close()
+
+
+def test_errors():
+    e = Engine(16, max_merges=4, table_slots=256)
+    with pytest.raises(CapacityError):
+        e.append_ids(np.arange(17, dtype=np.int32))
+    with pytest.raises(RuntimeError):
+        e.train(1)  # nothing counted yet
+    e.append_ids(np.array([1, 2, -3, 4], dtype=np.int32))
+    with pytest.raises(OverflowError):
+        e.count_initial()
+    e.reset()
+    e.append_ids(np.array([1, 2, 1, 2], dtype=np.int32))
+    e.count_initial()
+    with pytest.raises(OverflowError):
+        e.apply_merge(1, 2, 1 << 31)
+    with pytest.raises(ValueError):
+        e.append_ids(np.array([1, 2], dtype=np.int32), np.array([1, 2], dtype=np.int64))
+    e.close()
+    # a pair table that is too small reports the reference's capacity error
+    rng = np.random.default_rng(0)
+    e = Engine(1 << 16, max_merges=4, table_slots=256)
+    e.append_ids(rng.integers(0, 60000, 1 << 16).astype(np.int32))
+    with pytest.raises(CapacityError, match="capacity exceeded"):
+        e.count_initial()
+    e.close()

@@ -1,0 +1,107 @@
+"""The GPUBPETrainer drop-in against the reference's own results (tests/golden/train.json)."""
+import json
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from supertoken_b200 import GPUBPETrainer, synth
+from tests.helpers import corpus_rows, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def make_batch(rows):
+    """Padded batch as the reference's batchers build it (pad id -1, prefix-valid)."""
+    width = max(1, max((len(r) for r in rows), default=0))
+    tokens = torch.full((len(rows), width), -1, dtype=torch.int32)
+    valid = torch.zeros((len(rows), width), dtype=torch.uint8)
+    lengths = torch.zeros((len(rows),), dtype=torch.int32)
+    for i, r in enumerate(rows):
+        if len(r):
+            tokens[i, :len(r)] = torch.tensor(list(r), dtype=torch.int32)
+            valid[i, :len(r)] = 1
+            lengths[i] = len(r)
+    return tokens, valid, lengths
+
+
+def test_reference_unit_test_cases():
+    t = GPUBPETrainer(base_vocab=16, merges=1, device="cuda", randomize_ties=False)
+    t.fit([make_batch([[0, 1, 0, 1], [0, 2, 0, 2]])], log_every=100)
+    assert t.merges == [(0, 1)]
+    t = GPUBPETrainer(base_vocab=256, merges=1, device="cuda")
+    res = t.fit(iter([make_batch([[1, 2, 1, 2, 3], [1, 2, 4, 2]]), make_batch([[1, 2, 1, 2], [1, 2, 1, 2]])]),
+                log_every=10)
+    assert t.merges[:1] == [(1, 2)] and res["transfer_metrics"]["merge_stats"]
+    t = GPUBPETrainer(base_vocab=256, merges=3, device="cuda")
+    res = t.fit([make_batch([[1, 2, 3, 1, 2, 4], [1, 2, 3, 1, 2, 3], [1, 2, 4, 2, 4]])], log_every=10)
+    assert t.merges == [(1, 2), (256, 3), (256, 4)] and t.vocab_size == 259
+    assert set(res) == {"base_vocab", "vocab_size", "merges", "warm_start", "transfer_metrics", "telemetry"}
+    assert {"pair_count", "apply_merge", "host_sync"} <= set(res["telemetry"]["timings"])
+
+
+def test_seeded_tie_randomization():
+    batch = make_batch([[0, 1, 0, 1], [0, 2, 0, 2]])
+    runs = []
+    for seed in (123, 123, 456):
+        t = GPUBPETrainer(base_vocab=16, merges=1, device="cuda", randomize_ties=True, tie_seed=seed)
+        t.fit([batch], log_every=0)
+        runs.append(t.merges)
+    assert runs[0] == runs[1] and all(r in ([(0, 1)], [(0, 2)]) for r in runs)
+    # the pick is random.Random(seed).randrange(n) over the tied keys in ascending order
+    for seed, got in ((123, runs[0]), (456, runs[2])):
+        assert got == [[(0, 1), (0, 2)][random.Random(seed).randrange(2)]]
+
+
+def test_golden_trainer_fixtures_with_padding():
+    g = load_golden("train.json")
+    for case in g["random"] + g["adversarial"]:
+        rows = case["rows"]
+        nb = case.get("n_batches", 1)
+        per = max(1, (len(rows) + nb - 1) // nb)
+        batches = [make_batch(rows[i:i + per]) for i in range(0, len(rows), per)] or [make_batch([[]])]
+        t = GPUBPETrainer(base_vocab=case["base_vocab"], merges=case["target"], device="cuda")
+        t.fit(batches, log_every=0)
+        raw = [tuple(m) for m in case["merges_raw"]]
+        ids, off = O.flatten_rows(rows)
+        om, _, reason = O.train_flat(ids, off, case["base_vocab"], case["target"], 1)
+        assert t.merges[:len(om)] == raw[:len(om)] == om
+        assert len(t.merges) == len(raw)            # same stop / padding rule as the reference
+        assert t.vocab_size == case["vocab_size"]
+
+
+def test_padding_draws_follow_the_global_random_module():
+    rows = [[1, 2, 1, 2, 3], [7]]
+    random.seed(77)
+    t = GPUBPETrainer(base_vocab=256, merges=6, device="cuda")
+    t.fit([make_batch(rows)], log_every=0)
+    random.seed(77)
+    expect = [(1, 2)]
+    vocab = 257
+    while len(expect) < 6:
+        expect.append((random.randint(0, vocab - 1), random.randint(0, vocab - 1)))
+        vocab += 1
+    assert t.merges == expect and t.vocab_size == 262
+
+
+def test_fit_bytes_and_artifacts(tmp_path):
+    c = synth.config1_text(1 << 18, seed=3, file_bytes=1 << 14)
+    ids, off = O.flatten_rows(corpus_rows(c))
+    om, _, _ = O.train_flat(ids, off, 256, 64, 1)
+    t = GPUBPETrainer(merges=64, device="cuda:0")
+    res = t.fit_bytes(c.data, c.row_offsets)
+    assert res["merges"] == om and t.vocab_size == 320
+    paths = t.save_artifacts(tmp_path / "out")
+    lines = open(paths["merges"], encoding="utf-8").read().splitlines()
+    assert lines[0] == "#version: 0.2" and len(lines) == 65
+    vocab = json.load(open(paths["vocab"], encoding="utf-8"))
+    assert len(vocab) == 320
+    # checkpoint round trip + warm start from the checkpointed merges reproduces the run
+    t.save_checkpoint(tmp_path / "ck")
+    t2 = GPUBPETrainer(merges=64, device="cuda:0")
+    t2.load_checkpoint(tmp_path / "ck")
+    assert t2.merges == om
+    t3 = GPUBPETrainer(merges=64, device="cuda:0", warm_start_merges=om[:20])
+    assert t3.fit_bytes(c.data, c.row_offsets)["merges"] == om
