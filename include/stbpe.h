@@ -102,6 +102,12 @@ int stbpe_apply_merge(stbpe_engine *e, int32_t a, int32_t b, int32_t new_id, int
  * stop rule fires.  Synchronises the stream before returning. */
 int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream);
 
+/* stbpe_train with CUDA events around every kernel launch (no graph replay): kernel_ms[0..2]
+ * receive the summed device time of the select, merge and refresh kernels.  Measurement aid
+ * for the per-stage timings the reference records (gpu_tokenizer/bpe_trainer.py:4249-4260,
+ * :4385-4396). */
+int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *kernel_ms, void *stream);
+
 int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *stream);
 /* merges: 2*n int32 (a, b); counts: n int64 (may be NULL); live_before: n int64, live
  * tokens before each merge (may be NULL).  Host pointers. */

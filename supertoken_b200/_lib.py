@@ -9,7 +9,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libstbpe.so")
+LIB_PATH = os.environ.get("STBPE_LIB", os.path.join(_HERE, "libstbpe.so"))
 
 OK, E_BADARG, E_CAPACITY, E_TIMEOUT, E_CUDA, E_ID_OVERFLOW, E_STATE = range(7)
 RUNNING, STOP_TARGET, STOP_NO_PAIRS, STOP_LOW_COUNT, STOP_ERROR = range(5)
@@ -44,6 +44,7 @@ SIGNATURES = {
     "stbpe_select_best": (_int, [_vp, _P(ctypes.c_uint64), _P(_i64), _P(_i64), _vp]),
     "stbpe_apply_merge": (_int, [_vp, _i32, _i32, _i32, _P(_i64), _vp]),
     "stbpe_train": (_int, [_vp, _i32, _vp]),
+    "stbpe_train_timed": (_int, [_vp, _i32, _P(ctypes.c_float), _vp]),
     "stbpe_get_state": (_int, [_vp, _P(State), _vp]),
     "stbpe_get_merges": (_int, [_vp, _i32, _i32, _vp, _vp, _vp]),
     "stbpe_export_histogram": (_int, [_vp, _vp, _vp, _i64, _P(_i64), _vp]),

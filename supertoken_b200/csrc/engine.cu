@@ -191,15 +191,15 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaMemset"));
 
     // launch geometry: persistent CTAs, a whole number per SM
-    e->merge_slots = 2048;
+    e->merge_slots = 1024;
     e->count_slots = 8192;
-    e->merge_smem = (STBPE_TILE + 8) * sizeof(uint32_t) + (size_t)e->merge_slots * 12;
-    e->count_smem = (STBPE_TILE + 8) * sizeof(uint32_t) + (size_t)e->count_slots * 12;
+    e->merge_smem = TilePipe::bytes(e->merge_slots);
+    e->count_smem = TilePipe::bytes(e->count_slots);
     int occ = 0;
 #define SETUP(kern, smem, grid)                                                                         \
     c = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem));           \
     if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaFuncSetAttribute"));                         \
-    c = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, STBPE_NT, smem);                      \
+    c = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, STBPE_CTA_THREADS, smem);                      \
     if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaOccupancyMaxActiveBlocksPerMultiprocessor")); \
     grid = e->sm_count * (occ > 0 ? occ : 1)
     int g1 = 0, g2 = 0;
@@ -300,6 +300,7 @@ static int check_device_error(stbpe_engine *e, cudaStream_t s) {
         return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (pair table full)");
     if (err & STBPE_DERR_OUTBOX_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (delta outbox full)");
     if (err & STBPE_DERR_LTABLE_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (local delta table full)");
+    if (err & STBPE_DERR_TIMEOUT) return fail(e, STBPE_E_TIMEOUT, "a bounded device-side wait gave up (tile pipeline)");
     if (err & STBPE_DERR_KEY_MISSING) return fail(e, STBPE_E_STATE, "selected pair missing from the pair table");
     return STBPE_OK;
 }
@@ -335,9 +336,9 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
     if (e->d.n_tiles > 0) {
         int grid = e->count_grid < e->d.n_tiles ? e->count_grid : e->d.n_tiles;
         if (mg)
-            count_kernel<true><<<grid, STBPE_NT, e->count_smem, s>>>(e->d, e->count_slots);
+            count_kernel<true><<<grid, STBPE_CTA_THREADS, e->count_smem, s>>>(e->d, e->count_slots);
         else
-            count_kernel<false><<<grid, STBPE_NT, e->count_smem, s>>>(e->d, e->count_slots);
+            count_kernel<false><<<grid, STBPE_CTA_THREADS, e->count_smem, s>>>(e->d, e->count_slots);
         CK(cudaGetLastError());
     }
     return STBPE_OK;
@@ -388,9 +389,9 @@ static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s) {
     if (e->d.n_tiles > 0) {
         int grid = e->merge_grid < e->d.n_tiles ? e->merge_grid : e->d.n_tiles;
         if (mg)
-            merge_kernel<true><<<grid, STBPE_NT, e->merge_smem, s>>>(e->d, e->merge_slots);
+            merge_kernel<true><<<grid, STBPE_CTA_THREADS, e->merge_smem, s>>>(e->d, e->merge_slots);
         else
-            merge_kernel<false><<<grid, STBPE_NT, e->merge_smem, s>>>(e->d, e->merge_slots);
+            merge_kernel<false><<<grid, STBPE_CTA_THREADS, e->merge_smem, s>>>(e->d, e->merge_slots);
         CK(cudaGetLastError());
     }
     return STBPE_OK;
@@ -491,6 +492,54 @@ STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
         }
     }
     // one more selection decides the stop reason without applying anything when the target is reached
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(s));
+    return check_device_error(e, s);
+}
+
+// Same loop as stbpe_train, launched kernel by kernel with CUDA events around every launch so
+// that a caller can attribute device time to the three kernels (select / merge / refresh).
+STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *kernel_ms, void *stream) {
+    if (!e || n_merges < 0 || !kernel_ms) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->counted) return fail(e, STBPE_E_STATE, "count the pairs before training");
+    if (e->cfg.world_size > 1) return fail(e, STBPE_E_STATE, "single-rank entry point");
+    DevState h;
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    i64 target = (i64)h.merges_done + n_merges;
+    if (target > e->cfg.max_merges) target = e->cfg.max_merges;
+    set_target_kernel<<<1, 1, 0, s>>>(e->d, (int)target);
+    CK(cudaGetLastError());
+    const int todo = (int)(target - h.merges_done);
+    const int P = 128;
+    std::vector<cudaEvent_t> ev(4 * P);
+    for (auto &x : ev) CK(cudaEventCreate(&x));
+    kernel_ms[0] = kernel_ms[1] = kernel_ms[2] = 0.f;
+    int rc = STBPE_OK;
+    for (int base = 0; base < todo && rc == STBPE_OK; base += P) {
+        const int n = todo - base < P ? todo - base : P;
+        for (int i = 0; i < n && rc == STBPE_OK; ++i) {
+            cudaEventRecord(ev[4 * i], s);
+            select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+            cudaEventRecord(ev[4 * i + 1], s);
+            rc = launch_merge(e, false, s);
+            cudaEventRecord(ev[4 * i + 2], s);
+            if (rc == STBPE_OK) rc = launch_refresh(e, 0, s);
+            cudaEventRecord(ev[4 * i + 3], s);
+        }
+        cudaStreamSynchronize(s);
+        for (int i = 0; i < n && rc == STBPE_OK; ++i)
+            for (int k = 0; k < 3; ++k) {
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, ev[4 * i + k], ev[4 * i + k + 1]);
+                kernel_ms[k] += ms;
+            }
+    }
+    for (auto &x : ev) cudaEventDestroy(x);
+    if (rc != STBPE_OK) return rc;
     select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
     CK(cudaGetLastError());
     CK(cudaStreamSynchronize(s));

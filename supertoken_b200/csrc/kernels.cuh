@@ -56,7 +56,8 @@ __global__ void init_recs_kernel(EngineDev e, i64 n_tokens) {
     r.len = len;
     for (int i = 0; i < 3; ++i) r.head[i] = i < len ? e.tiles[base + i] : STBPE_NONE;
     r.tail = len > 0 ? e.tiles[base + len - 1] : STBPE_NONE;
-    r.pad[0] = r.pad[1] = 0;
+    r.tail2 = len > 1 ? e.tiles[base + len - 2] : STBPE_NONE;
+    r.pad = 0;
     e.recs[2 * t] = r;
     r.ver = -1;
     r.len = 0;
@@ -74,212 +75,7 @@ __global__ void clear_table_kernel(EngineDev e) {
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// K2  full adjacent-pair histogram (gpu_tokenizer/utils.py:558-635 without the sort)
-// Persistent CTAs walk tiles; every countable pair adds +1 into the CTA's shared-memory
-// table, which is flushed into the pair table (or the rank-local delta table) at the end.
-// ---------------------------------------------------------------------------------------
-template <bool MG>
-__global__ void __launch_bounds__(STBPE_NT, 2) count_kernel(EngineDev e, unsigned int smem_slots) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t *s_tok = reinterpret_cast<uint32_t *>(smem_raw);
-    SmemTable tab;
-    tab.keys = reinterpret_cast<u64 *>(smem_raw + (STBPE_TILE + 8) * sizeof(uint32_t));
-    tab.vals = reinterpret_cast<int *>(tab.keys + smem_slots);
-    tab.mask = smem_slots - 1;
-    smem_table_clear(tab);
-    const int m = 0x7FFFFFFF;  // any record version is "before" this
-    const int tid = threadIdx.x;
-    __syncthreads();
-    for (int tile = blockIdx.x; tile < e.n_tiles; tile += gridDim.x) {
-        TileRec rec;
-        current_rec(e, tile, m, rec);
-        const int len = rec.len;
-        if (len == 0) continue;
-        const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
-        for (int i = tid * 4; i < len; i += STBPE_NT * 4)
-            *reinterpret_cast<uint4 *>(s_tok + i) = *reinterpret_cast<const uint4 *>(g + i);
-        uint32_t prev, nxt[3];
-        if (tid == 0) gather_halo(e, tile, m, prev, nxt);
-        __syncthreads();
-        if (tid == 0) s_tok[len] = nxt[0];
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < STBPE_IPT; ++j) {
-            int p = j * STBPE_NT + tid;
-            if (p < len) {
-                uint32_t t0 = s_tok[p], t1 = s_tok[p + 1];
-                if (!(t1 & STBPE_FLAG)) {
-                    u64 key = ((u64)(t0 & STBPE_IDMASK) << 32) | (u64)t1;
-                    smem_table_add<MG>(tab, e, key, 1);
-                }
-            }
-        }
-        __syncthreads();
-    }
-    smem_table_flush<MG>(tab, e);
-}
-
-// ---------------------------------------------------------------------------------------
-// K3  one merge: find + rewrite + in-tile compaction + delta counts
-//
-// With M[i] = (id[i]==a && id[i+1]==b && token i+1 does not start a row) evaluated on
-// the pre-merge stream (gpu_tokenizer/utils.py:520-527), token i is dropped when M[i-1]
-// and becomes `new` when M[i] (utils.py:529-531).  The histogram of the result equals
-// the old histogram plus these local terms (x = live token before, y = after):
-//   every countable input pair (i,i+1) with M[i-1] | M[i] | M[i+1] ... -1, except the
-//     merged pair itself, whose table entry is zeroed when the merge is selected;
-//   a != b : M[i]            ... +1 (new, out[i+2]) if i+2 is in the row,
-//                                   out[i+2] = new when M[i+2]
-//            !M[i-1] & !M[i] ... +1 (id[i], new) when M[i+1]
-//   a == b : !M[i-1] & !M[i] ... +1 (id[i], new) when M[i+1]
-//            M[i-1] & !M[i]  ... +1 (new, id[i+1]) if i+1 is in the row   (tail of a run:
-//                                   the whole run collapses into ONE new token)
-// which is what a full recount of the rewritten rows gives.
-// ---------------------------------------------------------------------------------------
-template <bool MG>
-__global__ void __launch_bounds__(STBPE_NT, 2) merge_kernel(EngineDev e, unsigned int smem_slots) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ int s_wcnt[STBPE_IPT * STBPE_NW];
-    __shared__ uint32_t s_prev;
-    __shared__ int s_total;
-
-    DevState *st = e.st;
-    if (st->stopped) return;
-    const uint32_t a = (uint32_t)st->cur_a, b = (uint32_t)st->cur_b, nw = (uint32_t)st->cur_new;
-    const int m = st->merges_done;  // number of this merge (>= 1)
-    const bool same = (a == b);
-
-    uint32_t *s_tok = reinterpret_cast<uint32_t *>(smem_raw);
-    SmemTable tab;
-    tab.keys = reinterpret_cast<u64 *>(smem_raw + (STBPE_TILE + 8) * sizeof(uint32_t));
-    tab.vals = reinterpret_cast<int *>(tab.keys + smem_slots);
-    tab.mask = smem_slots - 1;
-    smem_table_clear(tab);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    i64 removed = 0, matches = 0;
-    __syncthreads();
-
-    for (int tile = blockIdx.x; tile < e.n_tiles; tile += gridDim.x) {
-        TileRec rec;
-        const int cur_slot = current_rec(e, tile, m, rec);
-        const int len = rec.len;
-        if (len == 0) continue;
-        uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
-        for (int i = tid * 4; i < len; i += STBPE_NT * 4)
-            *reinterpret_cast<uint4 *>(s_tok + i) = *reinterpret_cast<const uint4 *>(g + i);
-        uint32_t prev, nxt[3];
-        if (tid == 0) gather_halo(e, tile, m, prev, nxt);
-        __syncthreads();
-        if (tid == 0) {
-            s_prev = prev;
-            s_tok[len] = nxt[0];
-            s_tok[len + 1] = nxt[1];
-            s_tok[len + 2] = nxt[2];
-        }
-        __syncthreads();
-
-        uint32_t outv[STBPE_IPT];
-        unsigned int surv = 0;
-        int changed = 0, my_matches = 0;
-#pragma unroll
-        for (int j = 0; j < STBPE_IPT; ++j) {
-            const int p = j * STBPE_NT + tid;
-            outv[j] = 0;
-            if (p < len) {
-                const uint32_t tm1 = p ? s_tok[p - 1] : s_prev;
-                const uint32_t t0 = s_tok[p], t1 = s_tok[p + 1], t2 = s_tok[p + 2], t3 = s_tok[p + 3];
-                const uint32_t i0 = t0 & STBPE_IDMASK;
-                // a token following by a row start never matches: t1 == b is a compare of the
-                // whole word, so the flag bit must be clear
-                const bool M0 = (i0 == a) && (t1 == b);
-                const bool D0 = ((tm1 & STBPE_IDMASK) == a) && (t0 == b);
-                const bool M1 = ((t1 & STBPE_IDMASK) == a) && (t2 == b);
-                const bool pair01 = !(t1 & STBPE_FLAG);
-                if (pair01 && !M0 && (D0 || M1))
-                    smem_table_add<MG>(tab, e, ((u64)i0 << 32) | (u64)t1, -1);
-                if (!same) {
-                    if (M0) {
-                        if (!(t2 & STBPE_FLAG)) {
-                            const bool M2 = (t2 == a) && (t3 == b);
-                            smem_table_add<MG>(tab, e, ((u64)nw << 32) | (u64)(M2 ? nw : t2), 1);
-                        }
-                    } else if (!D0 && pair01 && M1) {
-                        smem_table_add<MG>(tab, e, ((u64)i0 << 32) | (u64)nw, 1);
-                    }
-                } else {
-                    if (!M0 && !D0) {
-                        if (pair01 && M1) smem_table_add<MG>(tab, e, ((u64)i0 << 32) | (u64)nw, 1);
-                    } else if (D0 && !M0) {
-                        if (pair01) smem_table_add<MG>(tab, e, ((u64)nw << 32) | (u64)t1, 1);
-                    }
-                }
-                outv[j] = M0 ? (nw | (t0 & STBPE_FLAG)) : t0;
-                if (!D0) surv |= 1u << j;
-                changed |= (int)(M0 | D0);
-                my_matches += (int)M0;
-            }
-        }
-        matches += my_matches;
-        // barrier: every thread has read its neighbourhood; also the "anything to do" vote
-        if (!__syncthreads_or(changed)) continue;
-
-        unsigned int bal[STBPE_IPT];
-#pragma unroll
-        for (int j = 0; j < STBPE_IPT; ++j) {
-            bal[j] = __ballot_sync(0xFFFFFFFFu, (surv >> j) & 1u);
-            if (lane == 0) s_wcnt[j * STBPE_NW + warp] = __popc(bal[j]);
-        }
-        __syncthreads();
-        if (warp == 0) {
-            // exclusive scan of the IPT*NW (=128) per-warp counts, 4 per lane
-            int v[4], sum = 0;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                v[q] = s_wcnt[lane * 4 + q];
-                sum += v[q];
-            }
-            int incl = sum;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                int n = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-                if (lane >= d) incl += n;
-            }
-            int run = incl - sum;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                s_wcnt[lane * 4 + q] = run;
-                run += v[q];
-            }
-            if (lane == 31) s_total = incl;
-        }
-        __syncthreads();
-        const unsigned int lt = (1u << lane) - 1u;
-#pragma unroll
-        for (int j = 0; j < STBPE_IPT; ++j)
-            if ((surv >> j) & 1u) s_tok[s_wcnt[j * STBPE_NW + warp] + __popc(bal[j] & lt)] = outv[j];
-        __syncthreads();
-        const int newlen = s_total;
-        for (int i = tid * 4; i < newlen; i += STBPE_NT * 4)
-            *reinterpret_cast<uint4 *>(g + i) = *reinterpret_cast<const uint4 *>(s_tok + i);
-        if (tid == 0) {
-            TileRec *dst = &e.recs[2 * tile + (cur_slot ^ 1)];
-            dst->len = newlen;
-            for (int i = 0; i < 3; ++i) dst->head[i] = i < newlen ? s_tok[i] : STBPE_NONE;
-            dst->tail = newlen > 0 ? s_tok[newlen - 1] : STBPE_NONE;
-            __threadfence();
-            dst->ver = m;
-            removed += len - newlen;
-        }
-        __syncthreads();
-    }
-    smem_table_flush<MG>(tab, e);
-    // warp-reduce the match count, one atomic per warp
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) matches += __shfl_down_sync(0xFFFFFFFFu, matches, d);
-    if (lane == 0 && matches) atomicAdd((u64 *)&st->n_matches, (u64)matches);
-    if (tid == 0 && removed) atomicAdd((u64 *)&st->n_live, (u64)(-removed));
-}
+#include "tile_kernels.cuh"
 
 // ---------------------------------------------------------------------------------------
 // K4  arg-max: block maxima refresh + reduction with the reference's tie-break

@@ -124,6 +124,12 @@ class Engine:
     def train(self, n_merges: int):
         self._check(self._lib.stbpe_train(self._h, int(n_merges), self._s))
 
+    def train_timed(self, n_merges: int):
+        """Like ``train`` but returns device milliseconds spent in (select, merge, refresh)."""
+        ms = (ctypes.c_float * 3)()
+        self._check(self._lib.stbpe_train_timed(self._h, int(n_merges), ms, self._s))
+        return float(ms[0]), float(ms[1]), float(ms[2])
+
     def state(self) -> L.State:
         st = L.State()
         self._check(self._lib.stbpe_get_state(self._h, ctypes.byref(st), self._s))
