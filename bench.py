@@ -308,7 +308,7 @@ def main():
         "vs_baseline": None, "dtype": "int32", "data": "synthetic",
         "config": {"workload": desc, "name": args.workload, "corpus_bytes": n_tokens, "rows": len(off_np) - 1,
                    "merges_timed": done, "first_merge": 0, "stop_reason": int(st.stop_reason),
-                   "l2": "inputs larger than L2 (4 bytes x tokens per merge)", "tile_tokens": 4096},
+                   "l2": "inputs larger than L2 (4 bytes x tokens per merge)", "tile_tokens": 1024},
         "pair_count": {"ms": count_ms, "gbs": 4.0 * n_tokens / (count_ms / 1e3) / 1e9,
                        "frac_of_measured_peak": 4.0 * n_tokens / (count_ms / 1e3) / 1e9 / peak,
                        "frac_of_8tbs": 4.0 * n_tokens / (count_ms / 1e3) / 1e9 / 8000.0,
