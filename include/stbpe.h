@@ -158,6 +158,26 @@ int stbpe_rows_count_pairs(const int32_t *tokens, const uint8_t *valid, int64_t 
 int stbpe_rows_apply_merge(int32_t *tokens, uint8_t *valid, int32_t *lengths, int64_t B, int64_t L,
                            int32_t a, int32_t b, int32_t new_id, uint8_t *spans, void *stream);
 
+/* stbpe_rows_count_pairs for callers that must not allocate device memory.  It has no
+ * counterpart in the reference.  Same inputs, outputs and result as stbpe_rows_count_pairs, but
+ * every temporary lives in one fixed block of device memory that is part of the library image
+ * (about 5.3 MB, held by every GPU that loads the library until the process exits); the call
+ * makes no cudaMalloc / cudaFree / cudaMallocAsync and calls no allocating library routine.
+ * Who needs it: a trainer that has already given all device memory to its preallocated
+ * workspaces (the reference fills the device up to its --target-util share before the merge
+ * loop, so a later allocation is the one that fails), and callers that keep several streams
+ * busy and cannot take the device-wide synchronisation a cudaMalloc / cudaFree implies.
+ * Limits and rules:
+ *   - B*(L-1) must not exceed 65 536 pair positions; larger batches get STBPE_E_CAPACITY and a
+ *     message in err (err may be NULL).  Nothing is computed in that case.
+ *   - The first call on each device looks up the block's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - All calls share the block, which keeps the previous call's contents; it is cleared at the
+ *     start of each call.  Calls that overlap on the GPU race: serialise them. */
+int stbpe_rows_count_pairs_noalloc(const int32_t *tokens, const uint8_t *valid, int64_t B, int64_t L,
+                                   int32_t *pair_keys, int64_t *pair_counts, int64_t cap,
+                                   int64_t *length_dev, void *stream, char *err, size_t err_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -57,6 +57,8 @@ SIGNATURES = {
     "stbpe_mg_candidate": (_int, [_vp, _vp, _vp]),
     "stbpe_mg_commit": (_int, [_vp, _vp, _vp]),
     "stbpe_rows_count_pairs": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
+    "stbpe_rows_count_pairs_noalloc": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp,
+                                              ctypes.c_char_p, ctypes.c_size_t]),
     "stbpe_rows_apply_merge": (_int, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _vp]),
 }
 

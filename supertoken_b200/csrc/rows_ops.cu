@@ -3,6 +3,8 @@
 #include <cub/device/device_radix_sort.cuh>
 #include <cuda_runtime.h>
 
+#include <cstdio>
+#include <mutex>
 #include <string>
 
 #include "../../include/stbpe.h"
@@ -291,3 +293,150 @@ STBPE_VISIBLE int stbpe_rows_apply_merge(int32_t *tokens, uint8_t *valid, int32_
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Pair counting for callers that must not allocate.
+//
+// stbpe_rows_count_pairs above takes its hash table, staging arrays and sort workspace from
+// the stream-ordered allocator on every call.  Two kinds of caller of this library cannot
+// afford that.  The reference's trainer sizes its batches to fill device memory (its
+// --target-util flag) and hands every byte to preallocated workspaces before the merge loop
+// starts, so an allocation made in the middle of the loop is the one that fails; and it
+// overlaps copies and kernels on three streams per device, which a cudaMalloc / cudaFree
+// stalls, because those calls synchronise the whole device.
+//
+// This variant works out of one fixed scratch block that is part of the library image: a
+// file-scope __device__ array.  Every GPU on which the library is loaded holds the block
+// (STBPE_STATIC_SCRATCH_BYTES, about 5.3 MB) from load to exit.  In host code the array's
+// name is only a handle for the runtime, not a device address, so the entry point asks
+// cudaGetSymbolAddress for the address once per device, with that device current, and hands
+// the returned pointer to the kernels.  That look-up happens inside the first call made on
+// each device; make that first call outside any stream capture.
+//
+// All calls share the block and it keeps what the last call left there: the table and the
+// counters are cleared at the start of every call, and two calls that overlap on the GPU
+// (different streams, or different host threads) race on it -- serialise them.
+// ---------------------------------------------------------------------------------------
+#define STBPE_STATIC_MAX_POSITIONS (1 << 16)  /* largest B*(L-1) accepted */
+#define STBPE_STATIC_TABLE_SLOTS (1 << 17)
+#define STBPE_STATIC_SORT_BYTES (1 << 20)
+#define STBPE_STATIC_SCRATCH_BYTES                                                              \
+    ((size_t)STBPE_STATIC_TABLE_SLOTS * sizeof(Slot) + (size_t)4 * STBPE_STATIC_MAX_POSITIONS * 8 + \
+     256 + (size_t)STBPE_STATIC_SORT_BYTES)
+
+static __device__ __align__(256) unsigned char g_static_scratch[STBPE_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+unsigned char *g_static_ptr[64] = {};
+
+// device address of the scratch block on the current device (looked up once per device)
+int static_scratch(unsigned char **out, char *err, size_t err_len) {
+    int dev = -1;
+    cudaError_t c = cudaGetDevice(&dev);
+    if (c != cudaSuccess || dev < 0 || dev >= 64) {
+        if (err) snprintf(err, err_len, "cudaGetDevice failed or device ordinal out of range: %s", cudaGetErrorString(c));
+        return STBPE_E_CUDA;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void *p = nullptr;
+        c = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (c != cudaSuccess || !p) {
+            if (err) snprintf(err, err_len, "cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(c));
+            cudaGetLastError();
+            return STBPE_E_CUDA;
+        }
+        g_static_ptr[dev] = static_cast<unsigned char *>(p);
+    }
+    *out = g_static_ptr[dev];
+    return STBPE_OK;
+}
+}  // namespace
+
+#define SCK(call)                                                                         \
+    do {                                                                                  \
+        cudaError_t c_ = (call);                                                          \
+        if (c_ != cudaSuccess) {                                                          \
+            if (err) snprintf(err, err_len, "%s: %s", #call, cudaGetErrorString(c_));     \
+            cudaGetLastError();                                                           \
+            return STBPE_E_CUDA;                                                          \
+        }                                                                                 \
+    } while (0)
+
+extern "C" STBPE_VISIBLE int stbpe_rows_count_pairs_noalloc(const int32_t *tokens, const uint8_t *valid,
+                                                            int64_t B, int64_t L, int32_t *pair_keys,
+                                                            int64_t *pair_counts, int64_t cap,
+                                                            int64_t *length_dev, void *stream, char *err,
+                                                            size_t err_len) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (err && err_len) err[0] = 0;
+    if (B < 0 || L < 0 || cap < 0) {
+        if (err) snprintf(err, err_len, "negative size");
+        return STBPE_E_BADARG;
+    }
+    const i64 total = (B > 0 && L > 1) ? B * (L - 1) : 0;
+    if (total > STBPE_STATIC_MAX_POSITIONS) {
+        if (err)
+            snprintf(err, err_len,
+                     "batch too large for the fixed scratch block: B*(L-1) = %lld pair positions, limit %d "
+                     "(use stbpe_rows_count_pairs, which allocates)",
+                     (long long)total, STBPE_STATIC_MAX_POSITIONS);
+        return STBPE_E_CAPACITY;
+    }
+    unsigned char *base = nullptr;
+    int rc = static_scratch(&base, err, err_len);
+    if (rc != STBPE_OK) return rc;
+    // carve the block: table | keys | counts | sorted keys | sorted counts | counters | sort workspace
+    Slot *table = reinterpret_cast<Slot *>(base);
+    u64 *keys = reinterpret_cast<u64 *>(base + (size_t)STBPE_STATIC_TABLE_SLOTS * sizeof(Slot));
+    i64 *counts = reinterpret_cast<i64 *>(keys + STBPE_STATIC_MAX_POSITIONS);
+    u64 *skeys = reinterpret_cast<u64 *>(counts + STBPE_STATIC_MAX_POSITIONS);
+    i64 *scounts = reinterpret_cast<i64 *>(skeys + STBPE_STATIC_MAX_POSITIONS);
+    u64 *meta = reinterpret_cast<u64 *>(scounts + STBPE_STATIC_MAX_POSITIONS);
+    void *sort_ws = reinterpret_cast<unsigned char *>(meta) + 256;
+    i64 n = 0;
+    if (total > 0) {
+        RowsTable t;
+        t.table = table;
+        t.mask = STBPE_STATIC_TABLE_SLOTS - 1;
+        t.n_keys = meta;
+        t.error = reinterpret_cast<unsigned int *>(meta + 1);
+        // the block still holds the previous call's table and counters: start from zero
+        SCK(cudaMemsetAsync(meta, 0, 256, s));
+        rows_clear_kernel<<<256, 256, 0, s>>>(t);
+        i64 blocks = (total + 255) / 256;
+        rows_count_kernel<<<(unsigned int)blocks, 256, 0, s>>>(tokens, valid, B, L, t);
+        SCK(cudaGetLastError());
+        u64 hmeta[2] = {0, 0};
+        SCK(cudaMemcpyAsync(hmeta, meta, sizeof(hmeta), cudaMemcpyDeviceToHost, s));
+        SCK(cudaStreamSynchronize(s));
+        n = (i64)hmeta[0];
+        if ((hmeta[1] & 0xFFFFFFFFull) != 0 || n > cap) {
+            if (err) snprintf(err, err_len, "pair workspace capacity exceeded (%lld unique pairs, cap %lld)", (long long)n, (long long)cap);
+            return STBPE_E_CAPACITY;
+        }
+        if (n > 0) {
+            SCK(cudaMemsetAsync(meta, 0, sizeof(u64), s));
+            rows_export_kernel<<<256, 256, 0, s>>>(t, keys, counts, meta, n);
+            size_t need = 0;
+            cub::DeviceRadixSort::SortPairs(nullptr, need, keys, skeys, counts, scounts, (int)n, 0, 64, s);
+            if (need > (size_t)STBPE_STATIC_SORT_BYTES) {
+                if (err) snprintf(err, err_len, "sort workspace of %zu bytes exceeds the reserved %d", need, STBPE_STATIC_SORT_BYTES);
+                return STBPE_E_CAPACITY;
+            }
+            cub::DeviceRadixSort::SortPairs(sort_ws, need, keys, skeys, counts, scounts, (int)n, 0, 64, s);
+            SCK(cudaGetLastError());
+        }
+    }
+    if (cap > 0) {
+        i64 blocks = (cap + 255) / 256;
+        if (blocks > 148 * 32) blocks = 148 * 32;
+        rows_write_kernel<<<(unsigned int)blocks, 256, 0, s>>>(skeys, scounts, n, pair_keys, (i64 *)pair_counts, cap, (i64 *)length_dev);
+        SCK(cudaGetLastError());
+    } else if (length_dev) {
+        SCK(cudaMemsetAsync(length_dev, 0, sizeof(i64), s));
+    }
+    SCK(cudaStreamSynchronize(s));
+    return STBPE_OK;
+}
