@@ -128,22 +128,32 @@ int stbpe_export_ties(stbpe_engine *e, int64_t count, uint64_t *keys, int64_t ca
 /* Export of the rewritten stream: ids (device, cap tokens, bit 31 = row start). */
 int stbpe_export_stream(stbpe_engine *e, int32_t *ids, int64_t cap, int64_t *n_out, void *stream);
 
-/* Multi-GPU exchange steps (one engine per rank; the collective itself is issued by
- * the host between these calls).  Replaces reduce_pair_histograms
- * (gpu_tokenizer/utils.py:863-978) with an exchange of deltas.
- *   stbpe_mg_outbox : device buffer [world_size][cap_per_peer] of (key, delta) 16-byte
- *                     entries preceded by a per-peer int64 count array.
- *   stbpe_mg_count_local / stbpe_mg_merge_local fill the outbox instead of the table;
- *   stbpe_mg_apply_inbox adds a received buffer of the same layout into the table slice;
- *   stbpe_mg_candidate writes this rank's best (key, count) to a device pointer;
- *   stbpe_mg_commit takes the winning (key, count) chosen identically on every rank. */
-int stbpe_mg_buffers(stbpe_engine *e, void **outbox, void **inbox, int64_t *cap_per_peer,
-                     int64_t *bytes_per_peer);
+/* Multi-GPU exchange steps (one engine per rank, created with world_size > 1; the collectives
+ * are issued by the host between these calls on the same stream).  Together they replace
+ * reduce_pair_histograms (gpu_tokenizer/utils.py:863-978): instead of gathering whole histograms,
+ * ranks exchange only the +-deltas of a merge, routed to the rank that owns the key
+ * (hash(key) % world_size).
+ *   stbpe_mg_set_buffers : caller-owned device buffers, each world_size chunks of
+ *                          (1 + cap_per_peer) 16-byte entries {key, delta}; entry 0 of a chunk
+ *                          holds the entry count.  outbox chunk p goes to rank p (all-to-all with
+ *                          equal splits), inbox chunk p comes from rank p.
+ *   stbpe_mg_count_local : local histogram of this rank's rows into the outbox (first round)
+ *   stbpe_mg_merge_local : apply the current merge to this rank's rows, deltas into the outbox;
+ *                          in an exchange-only round it just drains what earlier rounds kept
+ *   stbpe_mg_drain_only  : exchange-only round for the initial histogram
+ *   stbpe_mg_apply_inbox : add the received deltas into this rank's slice of the pair table
+ *   stbpe_mg_candidate   : this rank's best {key, count, incomplete, 0} (4 x int64, device)
+ *   stbpe_mg_commit      : takes the all-gathered candidates (world_size x 4 int64); every rank
+ *                          reaches the same decision: commit the best pair, stop, or - while any
+ *                          rank still holds deltas that did not fit a chunk - run another
+ *                          exchange-only round.  No host synchronisation is needed per merge. */
+int stbpe_mg_set_buffers(stbpe_engine *e, void *outbox, void *inbox, int64_t cap_per_peer);
 int stbpe_mg_count_local(stbpe_engine *e, void *stream);
+int stbpe_mg_drain_only(stbpe_engine *e, void *stream);
 int stbpe_mg_merge_local(stbpe_engine *e, void *stream);
 int stbpe_mg_apply_inbox(stbpe_engine *e, void *stream);
-int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev /* 2 x int64: key, count */, void *stream);
-int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev /* world x 2 int64 */, void *stream);
+int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev /* 4 x int64 */, void *stream);
+int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev /* world x 4 int64 */, void *stream);
 
 /* Stateless operators on padded [B, L] batches resident on the device, with the
  * reference's operator signatures.

@@ -50,7 +50,8 @@ SIGNATURES = {
     "stbpe_export_histogram": (_int, [_vp, _vp, _vp, _i64, _P(_i64), _vp]),
     "stbpe_export_ties": (_int, [_vp, _i64, _vp, _i64, _P(_i64), _vp]),
     "stbpe_export_stream": (_int, [_vp, _vp, _i64, _P(_i64), _vp]),
-    "stbpe_mg_buffers": (_int, [_vp, _P(_vp), _P(_vp), _P(_i64), _P(_i64)]),
+    "stbpe_mg_set_buffers": (_int, [_vp, _vp, _vp, _i64]),
+    "stbpe_mg_drain_only": (_int, [_vp, _vp]),
     "stbpe_mg_count_local": (_int, [_vp, _vp]),
     "stbpe_mg_merge_local": (_int, [_vp, _vp]),
     "stbpe_mg_apply_inbox": (_int, [_vp, _vp]),

@@ -66,9 +66,11 @@ struct DevState {
     u64 peek_key;
     i64 peek_count;
     i64 peek_ties;
-    unsigned int n_ltouched;
-    unsigned int ticket2;
+    unsigned int n_ltouched;   // entries of the rank-local delta table awaiting the drain
+    unsigned int n_lkept;      // entries the last drain had to keep (outbox chunk full)
     i64 export_n;
+    int exchange_only;         // multi-GPU: deltas still in flight, the next round only exchanges
+    int round_incomplete;      // multi-GPU: this rank saw a full chunk or kept entries this round
 };
 
 struct EngineDev {
@@ -89,7 +91,7 @@ struct EngineDev {
     int world, rank;
     Slot *ltable;
     u64 lmask;
-    unsigned int *ltouched;
+    unsigned int *ltouched;  // 2 lists of lslots entries: [0] filled by inserts, [1] by the drain
     Slot *outbox;  // [world][1 + cap] entries; entry 0 of a chunk = {count, 0}
     Slot *inbox;
     i64 cap_per_peer;

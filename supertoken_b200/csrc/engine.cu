@@ -171,11 +171,9 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     if (cfg->world_size > 1) {
         e->lslots = 1ull << 22;
         e->d.lmask = e->lslots - 1;
-        e->d.cap_per_peer = (i64)(1 << 18);
+        e->d.cap_per_peer = 0;  // exchange buffers are set by stbpe_mg_set_buffers
         ALLOC(e->d.ltable, e->lslots);
-        ALLOC(e->d.ltouched, e->lslots + 1);
-        ALLOC(e->d.outbox, (size_t)cfg->world_size * (e->d.cap_per_peer + 1));
-        ALLOC(e->d.inbox, (size_t)cfg->world_size * (e->d.cap_per_peer + 1));
+        ALLOC(e->d.ltouched, 2 * e->lslots);
         c = cudaMemset(e->d.ltable, 0xFF, e->lslots * sizeof(Slot));
         if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaMemset ltable"));
         // counts of the local table must start at zero (keys at EMPTY = all ones)
@@ -657,23 +655,22 @@ STBPE_VISIBLE int stbpe_export_stream(stbpe_engine *e, int32_t *ids, int64_t cap
 }
 
 // ------------------------------------------------------------------------------- multi-GPU
-STBPE_VISIBLE int stbpe_mg_buffers(stbpe_engine *e, void **outbox, void **inbox, int64_t *cap_per_peer,
-                                   int64_t *bytes_per_peer) {
-    if (!e) return STBPE_E_BADARG;
+STBPE_VISIBLE int stbpe_mg_set_buffers(stbpe_engine *e, void *outbox, void *inbox, int64_t cap_per_peer) {
+    if (!e || !outbox || !inbox || cap_per_peer < 1) return fail(e, STBPE_E_BADARG, "bad exchange buffers");
     if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
-    if (outbox) *outbox = e->d.outbox;
-    if (inbox) *inbox = e->d.inbox;
-    if (cap_per_peer) *cap_per_peer = e->d.cap_per_peer;
-    if (bytes_per_peer) *bytes_per_peer = (e->d.cap_per_peer + 1) * (i64)sizeof(Slot);
+    e->d.outbox = (Slot *)outbox;
+    e->d.inbox = (Slot *)inbox;
+    e->d.cap_per_peer = cap_per_peer;
     return STBPE_OK;
 }
 
 static int launch_drain(stbpe_engine *e, cudaStream_t s) {
+    if (!e->d.outbox || e->d.cap_per_peer < 1) return fail(e, STBPE_E_STATE, "call stbpe_mg_set_buffers first");
     outbox_reset_kernel<<<1, 64, 0, s>>>(e->d);
     CK(cudaGetLastError());
     drain_ltable_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
-    ltouched_reset_kernel<<<1, 1, 0, s>>>(e->d);
+    ltouched_swap_kernel<<<e->sm_count, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
     return STBPE_OK;
 }
@@ -689,6 +686,15 @@ STBPE_VISIBLE int stbpe_mg_count_local(stbpe_engine *e, void *stream) {
     if (rc != STBPE_OK) return rc;
     e->counted = true;
     return STBPE_OK;
+}
+
+// exchange-only round of the initial histogram: drains what the first round had to keep
+STBPE_VISIBLE int stbpe_mg_drain_only(stbpe_engine *e, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    return launch_drain(e, s);
 }
 
 STBPE_VISIBLE int stbpe_mg_merge_local(stbpe_engine *e, void *stream) {

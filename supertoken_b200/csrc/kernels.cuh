@@ -247,6 +247,8 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
     } else {
         cand[0] = (i64)bk;
         cand[1] = bc;
+        cand[2] = st->round_incomplete;
+        cand[3] = 0;
     }
 }
 
@@ -331,33 +333,56 @@ __global__ void outbox_reset_kernel(EngineDev e) {
         h.count = 0;
         e.outbox[(i64)p * (e.cap_per_peer + 1)] = h;
     }
-}
-
-__global__ void drain_ltable_kernel(EngineDev e) {
-    const unsigned int n = e.st->n_ltouched;
-    for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        Slot *s = &e.ltable[e.ltouched[i]];
-        const Slot v = *s;
-        s->key = STBPE_EMPTY;
-        s->count = 0;
-        if (v.count == 0) continue;
-        const int owner = owner_of(v.key, e.world);
-        Slot *chunk = e.outbox + (i64)owner * (e.cap_per_peer + 1);
-        const i64 j = (i64)atomicAdd(&chunk[0].key, 1ull);
-        if (j < e.cap_per_peer)
-            chunk[1 + j] = v;
-        else
-            atomicOr(&e.st->error, STBPE_DERR_OUTBOX_FULL);
+    if (p == 0) {
+        e.st->n_lkept = 0;
+        e.st->round_incomplete = 0;
     }
 }
 
-__global__ void ltouched_reset_kernel(EngineDev e) { e.st->n_ltouched = 0; }
+// Move the rank-local deltas into the per-owner outbox chunks.  A chunk holds cap_per_peer
+// entries; what does not fit stays in the local table and is listed again for the next round
+// (the header count of a chunk keeps counting past the capacity, which tells the receiver that
+// more is to come).
+__global__ void drain_ltable_kernel(EngineDev e) {
+    const unsigned int n = e.st->n_ltouched;
+    unsigned int *kept = e.ltouched + (e.lmask + 1);
+    for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const unsigned int idx = e.ltouched[i];
+        Slot *s = &e.ltable[idx];
+        const Slot v = *s;
+        if (v.count != 0) {
+            const int owner = owner_of(v.key, e.world);
+            Slot *chunk = e.outbox + (i64)owner * (e.cap_per_peer + 1);
+            const i64 j = (i64)atomicAdd(&chunk[0].key, 1ull);
+            if (j >= e.cap_per_peer) {
+                kept[atomicAdd(&e.st->n_lkept, 1u)] = idx;
+                e.st->round_incomplete = 1;
+                continue;
+            }
+            chunk[1 + j] = v;
+        }
+        s->key = STBPE_EMPTY;
+        s->count = 0;
+    }
+}
+
+// the kept entries become the list the next inserts append to
+__global__ void ltouched_swap_kernel(EngineDev e) {
+    const unsigned int n = e.st->n_lkept;
+    const unsigned int *kept = e.ltouched + (e.lmask + 1);
+    for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        e.ltouched[i] = kept[i];
+    if (blockIdx.x == 0 && threadIdx.x == 0) e.st->n_ltouched = n;
+}
 
 __global__ void apply_inbox_kernel(EngineDev e) {
     for (int p = 0; p < e.world; ++p) {
         const Slot *chunk = e.inbox + (i64)p * (e.cap_per_peer + 1);
         i64 n = (i64)chunk[0].key;
-        if (n > e.cap_per_peer) n = e.cap_per_peer;
+        if (n > e.cap_per_peer) {
+            n = e.cap_per_peer;
+            if (blockIdx.x == 0 && threadIdx.x == 0) e.st->round_incomplete = 1;
+        }
         for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) {
             const Slot v = chunk[1 + i];
             table_add(e, v.key, v.count);
@@ -365,19 +390,29 @@ __global__ void apply_inbox_kernel(EngineDev e) {
     }
 }
 
-// every rank evaluates the same candidates and reaches the same decision
+// Every rank evaluates the same gathered candidates {key, count, incomplete, -} and reaches the
+// same decision: if any rank still has deltas in flight the next round only exchanges, otherwise
+// the best candidate (highest count, smallest key) is committed or a stop rule fires.
 __global__ void commit_kernel(EngineDev e, const i64 *all_cands) {
     DevState *st = e.st;
     if (st->stopped) return;
     u64 bk = STBPE_EMPTY;
     i64 bc = 0;
+    bool incomplete = false;
     for (int r = 0; r < e.world; ++r) {
-        const u64 k = (u64)all_cands[2 * r];
-        const i64 c = all_cands[2 * r + 1];
+        const u64 k = (u64)all_cands[4 * r];
+        const i64 c = all_cands[4 * r + 1];
+        incomplete |= all_cands[4 * r + 2] != 0;
         if (c > 0 && better(k, c, bk, bc)) {
             bk = k;
             bc = c;
         }
     }
+    if (incomplete) {
+        st->n_dirty = 0;
+        st->exchange_only = 1;
+        return;
+    }
+    st->exchange_only = 0;
     advance_or_stop(e, bk, bc);
 }

@@ -315,7 +315,7 @@ template <bool MG>
 __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e, unsigned int smem_slots) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DevState *st = e.st;
-    if (st->stopped) return;
+    if (st->stopped || st->exchange_only) return;
     const uint32_t a = (uint32_t)st->cur_a, b = (uint32_t)st->cur_b, nw = (uint32_t)st->cur_new;
     const int m = st->merges_done;  // number of this merge (>= 1)
     const bool same = (a == b);

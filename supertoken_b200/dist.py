@@ -1,0 +1,309 @@
+"""Multi-GPU merge loop: rows sharded by contiguous document ranges, pair keys by hash owner.
+
+Replaces the reference's cross-rank histogram reduction (``utils.reduce_pair_histograms``,
+``gpu_tokenizer/utils.py:863-978``: all-gather of every rank's key list plus a dense all-reduce
+over the union, once per recount) with an exchange of the +-deltas of each merge:
+
+    round:  local merge kernel -> per-owner outbox chunks -> all-to-all (equal splits)
+            -> owners add into their table slice -> local best candidate
+            -> all-gather of ``world`` candidates -> every rank commits the same decision
+
+A chunk has a fixed capacity; deltas that do not fit stay on the sender and the candidates carry an
+"incomplete" flag, in which case every rank agrees to run another exchange-only round before a
+merge is chosen.  Nothing in a round needs the host to look at device data, so rounds are enqueued
+back to back and the host reads the state only every ``check_every`` rounds.
+
+The round logic is written against a small worker interface so that the same code drives
+(a) one ``EngineWorker`` per process over ``torch.distributed`` (NCCL), (b) several workers of one
+process on one GPU (tests: the device kernels of every rank run one after the other, no kernel
+waits for another), and (c) CPU stand-in workers over ``gloo`` (tests of the protocol itself).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib as L
+
+_M64 = (1 << 64) - 1
+
+
+def mix64(x: int) -> int:
+    """The 64-bit finaliser the kernels use to place and to own keys."""
+    x &= _M64
+    x ^= x >> 33
+    x = (x * 0xFF51AFD7ED558CCD) & _M64
+    x ^= x >> 33
+    x = (x * 0xC4CEB9FE1A85EC53) & _M64
+    x ^= x >> 33
+    return x
+
+
+def owner_of(key: int, world: int) -> int:
+    """Rank that owns a packed pair key (``owner_of`` in ``csrc/common.cuh``)."""
+    return (mix64(key) >> 40) % world
+
+
+def shard_rows(row_offsets: np.ndarray, world: int) -> List[Tuple[int, int]]:
+    """Contiguous row ranges ``[lo, hi)`` per rank, balanced by bytes; a row never spans ranks
+    (so no halo crosses GPUs).  The reference shards whole files per rank
+    (``gpu_tokenizer/cli_train_bpe.py:124-140``)."""
+    off = np.asarray(row_offsets, dtype=np.int64)
+    n_rows = len(off) - 1
+    total = int(off[-1] - off[0])
+    cuts = [0]
+    for r in range(1, world):
+        target = off[0] + total * r // world
+        k = int(np.searchsorted(off, target, side="left"))
+        cuts.append(min(max(k, cuts[-1]), n_rows))
+    cuts.append(n_rows)
+    return [(cuts[r], cuts[r + 1]) for r in range(world)]
+
+
+# ----------------------------------------------------------------------------- workers
+class EngineWorker:
+    """One rank's engine plus its exchange buffers (torch tensors on the engine's device)."""
+
+    def __init__(self, engine, cap_per_peer: int = 8192):
+        self.e = engine
+        self.world, self.rank = engine.world_size, engine.rank
+        self.cap = int(cap_per_peer)
+        dev = engine.device
+        shape = (self.world, self.cap + 1, 2)
+        self.outbox = torch.zeros(shape, dtype=torch.int64, device=dev)
+        self.inbox = torch.zeros(shape, dtype=torch.int64, device=dev)
+        self.cand = torch.zeros(4, dtype=torch.int64, device=dev)
+        self.all_cands = torch.zeros((self.world, 4), dtype=torch.int64, device=dev)
+        self._lib = L.load()
+        self._check(self._lib.stbpe_mg_set_buffers(engine._h, self.outbox.data_ptr(), self.inbox.data_ptr(), self.cap))
+
+    def _check(self, st):
+        self.e._check(st)
+
+    @property
+    def _s(self):
+        return self.e._s
+
+    def count_local(self):
+        with torch.cuda.device(self.e.device):
+            self._check(self._lib.stbpe_mg_count_local(self.e._h, self._s))
+
+    def merge_local(self):
+        with torch.cuda.device(self.e.device):
+            self._check(self._lib.stbpe_mg_merge_local(self.e._h, self._s))
+
+    def apply_inbox(self):
+        with torch.cuda.device(self.e.device):
+            self._check(self._lib.stbpe_mg_apply_inbox(self.e._h, self._s))
+
+    def candidate(self):
+        with torch.cuda.device(self.e.device):
+            self._check(self._lib.stbpe_mg_candidate(self.e._h, self.cand.data_ptr(), self._s))
+
+    def commit(self):
+        with torch.cuda.device(self.e.device):
+            self._check(self._lib.stbpe_mg_commit(self.e._h, self.all_cands.data_ptr(), self._s))
+
+    def progress(self) -> Tuple[int, int]:
+        """(merges done, stop reason); synchronises."""
+        st = self.e.state()
+        if st.device_error:
+            self.e.count_error()
+        return int(st.merges_done), int(st.stop_reason)
+
+    def merges(self):
+        return self.e.merges()
+
+
+class TorchDistComm:
+    """The two collectives of a round over ``torch.distributed`` (NCCL on GPUs, gloo in CPU tests)."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+
+    def exchange(self, workers: Sequence):
+        (w,) = workers
+        self.dist.all_to_all_single(w.inbox.view(-1), w.outbox.view(-1), group=self.group)
+
+    def gather(self, workers: Sequence):
+        (w,) = workers
+        self.dist.all_gather_into_tensor(w.all_cands.view(-1), w.cand, group=self.group)
+
+
+class LocalComm:
+    """All ranks live in this process (one GPU or CPU): chunks are copied between the workers."""
+
+    def exchange(self, workers: Sequence):
+        for dst in workers:
+            for src in workers:
+                dst.inbox[src.rank].copy_(src.outbox[dst.rank])
+
+    def gather(self, workers: Sequence):
+        for dst in workers:
+            for src in workers:
+                dst.all_cands[src.rank].copy_(src.cand)
+
+
+class ShardedBPE:
+    """Drives the rounds.  ``workers`` are the ranks that live in this process (normally one)."""
+
+    def __init__(self, workers: Sequence, comm):
+        self.workers = list(workers)
+        self.comm = comm
+        self.rounds = 0
+        self._counted = False
+
+    def _round(self, first: bool):
+        for w in self.workers:
+            w.count_local() if first else w.merge_local()
+        self.comm.exchange(self.workers)
+        for w in self.workers:
+            w.apply_inbox()
+            w.candidate()
+        self.comm.gather(self.workers)
+        for w in self.workers:
+            w.commit()
+        self.rounds += 1
+
+    def train(self, check_every: int = 64, max_rounds: Optional[int] = None):
+        """Run rounds until a stop rule fires on the device: the merge target the engines were
+        created with (``max_merges``), no pair left, or best count below 2.  A round applies the
+        merge committed by the previous round and commits the next one, so the last committed merge
+        is applied by one more round before the target stop is raised.  Returns (merges committed,
+        stop reason) as every rank sees them; the host reads device state only every
+        ``check_every`` rounds."""
+        budget = max_rounds if max_rounds is not None else 1 << 62
+        if not self._counted:
+            self._round(True)
+            self._counted = True
+            budget -= 1
+        while True:
+            done, reason = self.workers[0].progress()
+            if reason != L.RUNNING or budget <= 0:
+                return done, reason
+            n = min(check_every, budget)
+            for _ in range(n):
+                self._round(False)
+            budget -= n
+
+
+# ----------------------------------------------------------------------------- bench (N > 1)
+def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
+    """``bench.py`` at N > 1: the same corpus as N = 1, rows sharded over the ranks (strong
+    scaling), one process per GPU over NCCL.  Rank 0 prints the JSON line."""
+    import json
+    import time
+
+    import torch.distributed as dist
+
+    from . import synth
+    from .engine import Engine
+
+    gen, n_bytes, seed, merges, desc = wl
+    K, W = args.steps, args.warmup
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    corpus = getattr(synth, gen)(n_bytes=n_bytes, seed=seed, device=str(dev))
+    off = corpus.row_offsets.cpu().numpy()
+    lo, hi = shard_rows(off, world)[rank]
+    shard = corpus.data[off[lo]:off[hi]].clone()
+    shard_off = off[lo:hi + 1] - off[lo]
+    del corpus
+    torch.cuda.empty_cache()
+    n_local = int(shard.numel())
+
+    def make(max_merges):
+        e = Engine(max(n_local, 1), base_vocab=256, max_merges=max(max_merges, 1), device=dev,
+                   world_size=world, rank=rank)
+        return e, EngineWorker(e, cap_per_peer=8192)
+
+    def ev():
+        x = torch.cuda.Event(enable_timing=True)
+        x.record()
+        return x
+
+    def synced_max(ms: float) -> float:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # warm-up on a throw-away engine
+    e, w = make(W)
+    e.append_bytes(shard, shard_off)
+    ShardedBPE([w], TorchDistComm()).train(check_every=8)
+    e.close()
+    del e, w
+
+    e, w = make(K)
+    e.append_bytes(shard, shard_off)
+    loop = ShardedBPE([w], TorchDistComm())
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = ev()
+    loop._round(True)               # initial histogram + exchange + first decision
+    loop._counted = True
+    t1 = ev()
+    done, stop = loop.train(check_every=256)
+    t2 = ev()
+    torch.cuda.synchronize()
+    dist.barrier()
+    count_ms = synced_max(t0.elapsed_time(t1))
+    loop_ms = synced_max(t1.elapsed_time(t2))
+    merges_gpu, counts_gpu, live_before = e.merges(0, done)
+    live_all = torch.tensor(live_before.astype(np.float64).sum(), dtype=torch.float64, device=dev)
+    dist.all_reduce(live_all)
+    tokens_all = torch.tensor([float(n_local)], dtype=torch.float64, device=dev)
+    dist.all_reduce(tokens_all)
+    rounds = loop.rounds
+    e.close()
+    del e, w, loop
+
+    # end to end from pinned host memory through the same public pieces
+    host = torch.empty(n_local, dtype=torch.uint8, pin_memory=True)
+    host.copy_(shard)
+    torch.cuda.synchronize()
+    del shard
+    dist.barrier()
+    t = time.perf_counter()
+    e, w = make(K)
+    e.append_bytes(host, shard_off)
+    loop2 = ShardedBPE([w], TorchDistComm())
+    done2, _ = loop2.train(check_every=256)
+    m2, _, _ = e.merges(0, done2)
+    torch.cuda.synchronize()
+    e2e_s = synced_max((time.perf_counter() - t) * 1000.0) / 1000.0
+    assert m2 == merges_gpu, "merge list changed between two runs on the same input"
+
+    if rank == 0:
+        from bench import peaks  # type: ignore
+        peak, peak_kind = peaks()
+        algo = 4.0 * float(live_all.item())
+        line = {
+            "metric": "bpe_merges_per_sec", "value": done / (loop_ms / 1e3), "unit": "merges/s",
+            "n_gpus": world, "steps": done, "warmup": W, "ms_per_step": loop_ms / max(done, 1),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int32",
+            "data": "synthetic",
+            "config": {"workload": desc, "name": args.workload, "corpus_bytes": int(tokens_all.item()),
+                       "rows": len(off) - 1, "merges_timed": done, "first_merge": 0, "stop_reason": int(stop),
+                       "sharding": "contiguous document ranges by bytes; pair keys by hash owner",
+                       "rounds": rounds, "chunk_entries": 8192,
+                       "l2": "inputs larger than L2 (4 bytes x tokens per merge)", "tile_tokens": 1024},
+            "pair_count": {"ms": count_ms, "gbs": 4.0 * float(tokens_all.item()) / (count_ms / 1e3) / 1e9,
+                           "note": "local histogram + all-to-all + owner insert + first decision"},
+            "roofline": {"bound": "hbm", "kernel": "merge round (all kernels and both collectives)",
+                         "achieved": algo / (loop_ms / 1e3) / 1e9, "peak": peak * world, "peak_kind": peak_kind,
+                         "unit": "GB/s", "frac": algo / (loop_ms / 1e3) / 1e9 / (peak * world),
+                         "algorithmic_bytes": algo, "traffic": None},
+            "e2e": {"value": done2 / e2e_s, "unit": "merges/s", "seconds": e2e_s,
+                    "h2d_bytes_per_step": float(tokens_all.item()) / max(done2, 1), "d2h_bytes_per_step": 24.0},
+            "gpu_launches": rounds * 9,
+            "clocks": None, "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()

@@ -130,6 +130,19 @@ class Engine:
         self._check(self._lib.stbpe_train_timed(self._h, int(n_merges), ms, self._s))
         return float(ms[0]), float(ms[1]), float(ms[2])
 
+    def count_error(self):
+        """Raise the exception that matches the device error bits, if any are set."""
+        st = self.state()
+        bits = st.device_error
+        if bits & 32:
+            raise RuntimeError("a bounded device-side wait gave up (tile pipeline)")
+        if bits & (1 | 2 | 4):
+            raise CapacityError("pair workspace capacity exceeded (pair table / delta buffers full)")
+        if bits & 16:
+            raise OverflowError("Token id overflow: ids must be in [0, 2^31-2]")
+        if bits:
+            raise RuntimeError(f"device error bits {bits:#x}")
+
     def state(self) -> L.State:
         st = L.State()
         self._check(self._lib.stbpe_get_state(self._h, ctypes.byref(st), self._s))

@@ -1,0 +1,99 @@
+"""Multi-rank engine kernels (rank-local delta table, per-owner outbox, inbox apply, candidate,
+commit) against the single-process oracle.  With one GPU the ranks are emulated as several engines
+of one process whose kernels run one after the other (LocalComm copies the chunks); with two or
+more GPUs the same loop runs as one process per GPU over NCCL."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from supertoken_b200 import _lib as L
+from supertoken_b200 import synth
+from supertoken_b200.dist import EngineWorker, LocalComm, ShardedBPE, TorchDistComm, shard_rows
+from supertoken_b200.engine import Engine
+from tests.helpers import corpus_rows
+
+pytestmark = pytest.mark.gpu
+
+
+def _make_worker(data, off, lo, hi, rank, world, target, cap, device="cuda"):
+    n = int(off[hi] - off[lo])
+    e = Engine(max(n, 1), base_vocab=256, max_merges=target, device=device, table_slots=1 << 18,
+               world_size=world, rank=rank)
+    if n:
+        e.append_bytes(data[off[lo]:off[hi]], off[lo:hi + 1] - off[lo])
+    return EngineWorker(e, cap_per_peer=cap)
+
+
+@pytest.mark.parametrize("world,cap", [(2, 8192), (3, 40), (4, 500)])
+def test_emulated_ranks_on_one_gpu_match_oracle(world, cap):
+    c = synth.config5_adversarial(1 << 20, seed=11)
+    rows = corpus_rows(c)
+    off = np.asarray(c.row_offsets)
+    target = 60
+    om, oc, _ = O.train_flat(*O.flatten_rows(rows), 256, target, 1)
+    workers = [_make_worker(c.data, off, lo, hi, r, world, target, cap)
+               for r, (lo, hi) in enumerate(shard_rows(off, world))]
+    loop = ShardedBPE(workers, LocalComm())
+    done, stop = loop.train(check_every=16)
+    assert done == target and stop == L.STOP_TARGET
+    for w in workers:
+        m, cnt, _ = w.merges()
+        assert m == om and cnt.tolist() == oc
+    if cap < 100:
+        assert loop.rounds > target + 1   # small chunks forced exchange-only rounds
+    # the union of the owners' table slices is the histogram of the rewritten corpus
+    ids, o2 = O.flatten_rows(rows)
+    for i, (a, b) in enumerate(om):
+        O.apply_merge_flat(ids, o2, a, b, 256 + i)
+    ok, okc = O.count_pairs_flat(ids[:o2[-1]].copy(), o2, 1)
+    got = {}
+    for w in workers:
+        k, cnt = w.e.export_histogram()
+        for kk, cc in zip(k.cpu().numpy().astype(np.uint64).tolist(), cnt.cpu().tolist()):
+            assert kk not in got
+            got[kk] = cc
+    assert got == dict(zip(ok.tolist(), okc.tolist()))
+    for w in workers:
+        w.e.close()
+
+
+def _nccl_rank(rank, world, port, target, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        c = synth.config2_mixed(2 << 20, seed=3, lexicon=5000, mean_doc_bytes=2048)
+        off = np.asarray(c.row_offsets)
+        lo, hi = shard_rows(off, world)[rank]
+        w = _make_worker(c.data, off, lo, hi, rank, world, target, 4096, device=f"cuda:{rank}")
+        done, stop = ShardedBPE([w], TorchDistComm()).train(check_every=32)
+        m, cnt, _ = w.merges()
+        q.put((rank, m, cnt.tolist(), done, stop))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_over_nccl_match_oracle():
+    import torch.multiprocessing as mp
+    world, target = 2, 80
+    c = synth.config2_mixed(2 << 20, seed=3, lexicon=5000, mean_doc_bytes=2048)
+    om, oc, _ = O.train_flat(*O.flatten_rows(corpus_rows(c)), 256, target, 1)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, target, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, m, cnt, done, stop in results:
+        assert m == om and cnt == oc and done == target and stop == L.STOP_TARGET
