@@ -266,7 +266,7 @@ def main():
     # per-kernel device time of the same K merges (events around every launch)
     load()
     eng.count_initial()
-    sel_ms, mrg_ms, ref_ms = eng.train_timed(K)
+    sel_ms, mrg_ms, ref_ms, repack_ms = eng.train_timed(K)
     torch.cuda.synchronize()
     merges_again, _, _ = eng.merges(0, eng.state().merges_done)
     assert merges_again == merges_gpu, "merge list changed between two runs on the same input"
@@ -316,7 +316,7 @@ def main():
         "roofline": {"bound": "hbm", "kernel": "merge_kernel", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "algorithmic_bytes": algo_bytes, "kernel_ms": mrg_ms, "launches": done,
-                     "other_kernels_ms": {"select_kernel": sel_ms, "refresh_kernel": ref_ms},
+                     "other_kernels_ms": {"select_kernel": sel_ms, "refresh_kernel": ref_ms, "repack": repack_ms},
                      "traffic": None},
         "e2e": {"value": e2e, "unit": "merges/s", "seconds": e2e_s,
                 "h2d_bytes_per_step": (n_tokens + off_np.nbytes) / max(len(learned), 1),

@@ -102,11 +102,17 @@ int stbpe_apply_merge(stbpe_engine *e, int32_t a, int32_t b, int32_t new_id, int
  * stop rule fires.  Synchronises the stream before returning. */
 int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream);
 
-/* stbpe_train with CUDA events around every kernel launch (no graph replay): kernel_ms[0..2]
- * receive the summed device time of the select, merge and refresh kernels.  Measurement aid
+/* stbpe_train with CUDA events around every kernel launch (no graph replay): kernel_ms[0..3]
+ * receive the summed device time of the select, merge and refresh kernels and of the re-packs.  Measurement aid
  * for the per-stage timings the reference records (gpu_tokenizer/bpe_trainer.py:4249-4260,
  * :4385-4396). */
 int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *kernel_ms, void *stream);
+
+/* Dense re-pack of the token stream (tiles only shrink; stbpe_train does this by itself whenever
+ * at most half of the tile capacity in use is live).  force != 0 re-packs regardless.  *did (may
+ * be NULL) reports whether it happened.  Replaces nothing in the reference, whose rows are
+ * re-compacted by every merge (gpu_tokenizer/utils.py:347-410). */
+int stbpe_repack(stbpe_engine *e, int force, int *did, void *stream);
 
 int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *stream);
 /* merges: 2*n int32 (a, b); counts: n int64 (may be NULL); live_before: n int64, live

@@ -45,6 +45,7 @@ SIGNATURES = {
     "stbpe_apply_merge": (_int, [_vp, _i32, _i32, _i32, _P(_i64), _vp]),
     "stbpe_train": (_int, [_vp, _i32, _vp]),
     "stbpe_train_timed": (_int, [_vp, _i32, _P(ctypes.c_float), _vp]),
+    "stbpe_repack": (_int, [_vp, _int, _P(_int), _vp]),
     "stbpe_get_state": (_int, [_vp, _P(State), _vp]),
     "stbpe_get_merges": (_int, [_vp, _i32, _i32, _vp, _vp, _vp]),
     "stbpe_export_histogram": (_int, [_vp, _vp, _vp, _i64, _P(_i64), _vp]),

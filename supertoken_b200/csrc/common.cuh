@@ -14,8 +14,9 @@
 //                  version below m, which nobody writes during merge m.
 //   pair table   : open addressing, linear probing, 16-byte slots {key = (a<<32)|b,
 //                  int64 count}.  Keys are never removed; a count may return to zero.
-//   block maxima : best (count, smallest key) of every block of 256 slots; only blocks
-//                  touched by a merge are recomputed, the arg-max reduces the maxima.
+//   block maxima : best (count, smallest key) of every block of 256 slots, and of every
+//                  256 blocks above that; only blocks touched by a merge are recomputed, the
+//                  arg-max reduces the few top-level maxima.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -69,6 +70,8 @@ struct DevState {
     unsigned int n_ltouched;   // entries of the rank-local delta table awaiting the drain
     unsigned int n_lkept;      // entries the last drain had to keep (outbox chunk full)
     i64 export_n;
+    unsigned int n_dirty2;     // super-blocks whose maximum must be recomputed
+    unsigned int pad1;
     int exchange_only;         // multi-GPU: deltas still in flight, the next round only exchanges
     int round_incomplete;      // multi-GPU: this rank saw a full chunk or kept entries this round
 };
@@ -83,6 +86,10 @@ struct EngineDev {
     unsigned int *dirty_flag;
     unsigned int *dirty_list;
     unsigned int n_blocks;
+    Slot *supermax;             // best entry of every 256 blocks (second level of the arg-max)
+    unsigned int *dirty2_flag;
+    unsigned int *dirty2_list;
+    unsigned int n_super2;
     DevState *st;
     int32_t *merges;
     i64 *merge_counts;

@@ -1,5 +1,6 @@
 // Host side of the C ABI declared in include/stbpe.h: memory, launches, CUDA graphs.
 #include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -27,8 +28,11 @@ struct stbpe_engine {
     unsigned int merge_slots, count_slots;
     size_t merge_smem, count_smem;
     bool recs_stale, counted;
+    uint32_t *tiles_alt;  // second stream buffer, allocated at the first re-pack
+    int repacks;
     cudaGraphExec_t graph;
     int graph_merges;
+    uint32_t *graph_tiles;
     cudaStream_t graph_stream;
     bool use_graph;
     std::string err;
@@ -125,6 +129,8 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->cfg = *cfg;
     e->graph = nullptr;
     e->graph_merges = 0;
+    e->tiles_alt = nullptr;
+    e->repacks = 0;
     e->use_graph = getenv("STBPE_NO_GRAPH") == nullptr;
     memset(&e->d, 0, sizeof(e->d));
     auto bail = [&](int code) {
@@ -162,6 +168,10 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     ALLOC(e->d.blockmax, e->d.n_blocks);
     ALLOC(e->d.dirty_flag, e->d.n_blocks);
     ALLOC(e->d.dirty_list, e->d.n_blocks);
+    e->d.n_super2 = (e->d.n_blocks + 255) / 256;
+    ALLOC(e->d.supermax, e->d.n_super2);
+    ALLOC(e->d.dirty2_flag, e->d.n_super2);
+    ALLOC(e->d.dirty2_list, e->d.n_super2);
     ALLOC(e->d.st, 1);
     ALLOC(e->d.merges, (size_t)2 * (cfg->max_merges + 1));
     ALLOC(e->d.merge_counts, (size_t)cfg->max_merges + 1);
@@ -186,6 +196,8 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     }
 #undef ALLOC
     c = cudaMemset(e->d.dirty_flag, 0, e->d.n_blocks * sizeof(unsigned int));
+    if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaMemset"));
+    c = cudaMemset(e->d.dirty2_flag, 0, e->d.n_super2 * sizeof(unsigned int));
     if (c != cudaSuccess) return bail(cuda_fail(e, c, "cudaMemset"));
 
     // launch geometry: persistent CTAs, a whole number per SM
@@ -329,7 +341,11 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
     clear_table_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
     CK(cudaMemsetAsync(e->d.dirty_flag, 0, e->d.n_blocks * sizeof(unsigned int), s));
+    CK(cudaMemsetAsync(e->d.dirty2_flag, 0, e->d.n_super2 * sizeof(unsigned int), s));
+    CK(cudaMemsetAsync(e->d.blockmax, 0, (size_t)e->d.n_blocks * sizeof(Slot), s));  // count 0 = no candidate
+    CK(cudaMemsetAsync(e->d.supermax, 0, (size_t)e->d.n_super2 * sizeof(Slot), s));
     CK(cudaMemsetAsync(&e->d.st->n_dirty, 0, sizeof(unsigned int), s));
+    CK(cudaMemsetAsync(&e->d.st->n_dirty2, 0, sizeof(unsigned int), s));
     CK(cudaMemsetAsync(&e->d.st->n_keys, 0, sizeof(u64), s));
     if (e->d.n_tiles > 0) {
         int grid = e->count_grid < e->d.n_tiles ? e->count_grid : e->d.n_tiles;
@@ -345,6 +361,11 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
 static int launch_refresh(stbpe_engine *e, int all, cudaStream_t s) {
     refresh_kernel<<<e->refresh_grid, 256, 0, s>>>(e->d, all);
     CK(cudaGetLastError());
+    if (all) {  // rebuild the second level as well (a peek changes nothing else)
+        CK(cudaMemsetAsync(e->d.dirty2_flag, 0, e->d.n_super2 * sizeof(unsigned int), s));
+        select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 0, 1, e->cand);
+        CK(cudaGetLastError());
+    }
     return STBPE_OK;
 }
 
@@ -367,7 +388,7 @@ STBPE_VISIBLE int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *cou
     cudaStream_t s = (cudaStream_t)stream;
     CK(cudaSetDevice(e->cfg.device));
     if (!e->counted) return fail(e, STBPE_E_STATE, "count the pairs before selecting");
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 0, e->partial, e->cand);
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 0, 0, e->cand);
     CK(cudaGetLastError());
     if (n_ties) {
         CK(cudaMemsetAsync(&e->d.st->peek_ties, 0, sizeof(i64), s));
@@ -420,6 +441,58 @@ STBPE_VISIBLE int stbpe_apply_merge(stbpe_engine *e, int32_t a, int32_t b, int32
     return check_device_error(e, s);
 }
 
+// Dense re-pack of the stream when at most three quarters of the tile capacity in use is live.
+// Synchronises the stream.  *did (may be NULL) tells whether a re-pack happened.
+static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
+    if (did) *did = 0;
+    const int nt = e->d.n_tiles;
+    if (nt < 2 || e->recs_stale) return STBPE_OK;
+    DevState h;
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    if (!force && (h.n_live * 4 > (i64)nt * STBPE_TILE * 3 || nt < 64)) return STBPE_OK;  // re-pack at <= 75 % fill
+    if (!e->tiles_alt) CK(dev_alloc(e, &e->tiles_alt, (size_t)e->max_tiles * STBPE_TILE));
+    i64 *lens = nullptr, *offs = nullptr;
+    CK(cudaMallocAsync((void **)&lens, (size_t)(nt + 1) * sizeof(i64), s));
+    CK(cudaMallocAsync((void **)&offs, (size_t)(nt + 1) * sizeof(i64), s));
+    CK(cudaMemsetAsync(lens + nt, 0, sizeof(i64), s));
+    tile_lens_kernel<<<(nt + 255) / 256, 256, 0, s>>>(e->d, lens);
+    CK(cudaGetLastError());
+    size_t tmp_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, lens, offs, nt + 1, s);
+    void *tmp = nullptr;
+    CK(cudaMallocAsync(&tmp, tmp_bytes ? tmp_bytes : 16, s));
+    cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, lens, offs, nt + 1, s);
+    CK(cudaGetLastError());
+    repack_copy_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, offs, e->tiles_alt);
+    CK(cudaGetLastError());
+    i64 total = 0;
+    CK(cudaMemcpyAsync(&total, offs + nt, sizeof(i64), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    CK(cudaFreeAsync(lens, s));
+    CK(cudaFreeAsync(offs, s));
+    CK(cudaFreeAsync(tmp, s));
+    uint32_t *old = e->d.tiles;
+    e->d.tiles = e->tiles_alt;
+    e->tiles_alt = old;
+    e->d.n_tiles = (int)((total + STBPE_TILE - 1) / STBPE_TILE);
+    e->n_tokens = total;  // capacity in use; the merge log keeps the live counts
+    if (e->d.n_tiles > 0) {
+        init_recs_kernel<<<(e->d.n_tiles + 255) / 256, 256, 0, s>>>(e->d, total);
+        CK(cudaGetLastError());
+    }
+    CK(cudaStreamSynchronize(s));
+    e->repacks++;
+    if (did) *did = 1;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_repack(stbpe_engine *e, int force, int *did, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    CK(cudaSetDevice(e->cfg.device));
+    return maybe_repack(e, force != 0, did, (cudaStream_t)stream);
+}
+
 __global__ void set_target_kernel(EngineDev e, int target) {
     e.st->target = target;
     e.st->stopped = 0;
@@ -428,7 +501,7 @@ __global__ void set_target_kernel(EngineDev e, int target) {
 }
 
 static int enqueue_iteration(stbpe_engine *e, cudaStream_t s) {
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
     CK(cudaGetLastError());
     int rc = launch_merge(e, false, s);
     if (rc != STBPE_OK) return rc;
@@ -449,48 +522,60 @@ STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
     set_target_kernel<<<1, 1, 0, s>>>(e->d, (int)target);
     CK(cudaGetLastError());
     int todo = (int)(target - h.merges_done);
-    const int G = 32;
-    if (e->use_graph && todo >= G) {
-        // the kernels take all their work from device state, so one captured batch of G
-        // iterations is replayed; iterations past a stop rule return immediately
-        if (e->graph && (e->graph_merges != e->d.n_tiles)) {
-            cudaGraphExecDestroy(e->graph);
-            e->graph = nullptr;
-        }
-        if (!e->graph) {
-            cudaStream_t cs;
-            CK(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
-            cudaGraph_t g;
-            CK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
-            int rc = STBPE_OK;
-            for (int i = 0; i < G && rc == STBPE_OK; ++i) rc = enqueue_iteration(e, cs);
-            cudaError_t ce = cudaStreamEndCapture(cs, &g);
-            if (rc != STBPE_OK) {
-                cudaStreamDestroy(cs);
-                return rc;
+    const int G = 32, CHECK = 256;  // merges per graph replay / per look at the device state
+    while (todo > 0) {
+        int rc = maybe_repack(e, false, nullptr, s);
+        if (rc != STBPE_OK) return rc;
+        int batch = todo < CHECK ? todo : CHECK;
+        todo -= batch;
+        if (e->use_graph && batch >= G) {
+            // the kernels take all their work from device state, so one captured batch of G
+            // iterations is replayed; iterations past a stop rule return immediately
+            if (e->graph && (e->graph_merges != e->d.n_tiles || e->graph_tiles != e->d.tiles)) {
+                cudaGraphExecDestroy(e->graph);
+                e->graph = nullptr;
             }
-            if (ce != cudaSuccess) {
+            if (!e->graph) {
+                cudaStream_t cs;
+                CK(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
+                cudaGraph_t g;
+                CK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+                int rc2 = STBPE_OK;
+                for (int i = 0; i < G && rc2 == STBPE_OK; ++i) rc2 = enqueue_iteration(e, cs);
+                cudaError_t ce = cudaStreamEndCapture(cs, &g);
+                if (rc2 != STBPE_OK) {
+                    cudaStreamDestroy(cs);
+                    return rc2;
+                }
+                if (ce != cudaSuccess) {
+                    cudaStreamDestroy(cs);
+                    return cuda_fail(e, ce, "cudaStreamEndCapture");
+                }
+                ce = cudaGraphInstantiate(&e->graph, g, 0);
+                cudaGraphDestroy(g);
                 cudaStreamDestroy(cs);
-                return cuda_fail(e, ce, "cudaStreamEndCapture");
+                if (ce != cudaSuccess) return cuda_fail(e, ce, "cudaGraphInstantiate");
+                e->graph_merges = e->d.n_tiles;  // the capture froze the stream pointer, n_tiles and the grids
+                e->graph_tiles = e->d.tiles;
             }
-            ce = cudaGraphInstantiate(&e->graph, g, 0);
-            cudaGraphDestroy(g);
-            cudaStreamDestroy(cs);
-            if (ce != cudaSuccess) return cuda_fail(e, ce, "cudaGraphInstantiate");
-            e->graph_merges = e->d.n_tiles;  // the capture froze n_tiles and the grids
+            while (batch > 0) {
+                CK(cudaGraphLaunch(e->graph, s));
+                batch -= G;
+            }
+        } else {
+            for (int i = 0; i < batch; ++i) {
+                rc = enqueue_iteration(e, s);
+                if (rc != STBPE_OK) return rc;
+            }
         }
-        while (todo > 0) {
-            CK(cudaGraphLaunch(e->graph, s));
-            todo -= G;
-        }
-    } else {
-        for (int i = 0; i < todo; ++i) {
-            int rc = enqueue_iteration(e, s);
-            if (rc != STBPE_OK) return rc;
+        if (todo > 0) {  // stop early when a stop rule fired
+            CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+            CK(cudaStreamSynchronize(s));
+            if (h.stopped) break;
         }
     }
     // one more selection decides the stop reason without applying anything when the target is reached
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
     CK(cudaGetLastError());
     CK(cudaStreamSynchronize(s));
     return check_device_error(e, s);
@@ -515,13 +600,29 @@ STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *ke
     const int P = 128;
     std::vector<cudaEvent_t> ev(4 * P);
     for (auto &x : ev) CK(cudaEventCreate(&x));
-    kernel_ms[0] = kernel_ms[1] = kernel_ms[2] = 0.f;
+    kernel_ms[0] = kernel_ms[1] = kernel_ms[2] = kernel_ms[3] = 0.f;
     int rc = STBPE_OK;
+    cudaEvent_t r0, r1;
+    CK(cudaEventCreate(&r0));
+    CK(cudaEventCreate(&r1));
     for (int base = 0; base < todo && rc == STBPE_OK; base += P) {
         const int n = todo - base < P ? todo - base : P;
+        if (base % 256 == 0) {
+            int did = 0;
+            cudaEventRecord(r0, s);
+            rc = maybe_repack(e, false, &did, s);
+            cudaEventRecord(r1, s);
+            cudaEventSynchronize(r1);
+            if (did) {
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, r0, r1);
+                kernel_ms[3] += ms;
+            }
+            if (rc != STBPE_OK) break;
+        }
         for (int i = 0; i < n && rc == STBPE_OK; ++i) {
             cudaEventRecord(ev[4 * i], s);
-            select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+            select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
             cudaEventRecord(ev[4 * i + 1], s);
             rc = launch_merge(e, false, s);
             cudaEventRecord(ev[4 * i + 2], s);
@@ -537,8 +638,10 @@ STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *ke
             }
     }
     for (auto &x : ev) cudaEventDestroy(x);
+    cudaEventDestroy(r0);
+    cudaEventDestroy(r1);
     if (rc != STBPE_OK) return rc;
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, e->partial, e->cand);
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
     CK(cudaGetLastError());
     CK(cudaStreamSynchronize(s));
     return check_device_error(e, s);
@@ -721,7 +824,7 @@ STBPE_VISIBLE int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev, void *stre
     if (!e || !cand_dev) return STBPE_E_BADARG;
     cudaStream_t s = (cudaStream_t)stream;
     CK(cudaSetDevice(e->cfg.device));
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 2, e->partial, (i64 *)cand_dev);
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 2, 0, (i64 *)cand_dev);
     CK(cudaGetLastError());
     return STBPE_OK;
 }

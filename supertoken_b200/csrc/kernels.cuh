@@ -115,6 +115,8 @@ __global__ void refresh_kernel(EngineDev e, int all) {
             s.count = bc;
             e.blockmax[blk] = s;
             e.dirty_flag[blk] = 0u;
+            const unsigned int sb = blk >> 8;
+            if (!all && atomicExch(&e.dirty2_flag[sb], 1u) == 0u) e.dirty2_list[atomicAdd(&e.st->n_dirty2, 1u)] = sb;
         }
     }
 }
@@ -175,27 +177,12 @@ __device__ __forceinline__ void advance_or_stop(const EngineDev &e, u64 key, i64
     }
 }
 
-// mode 0: peek (result into st->peek_*), 1: advance the loop, 2: write candidate to cand[0..1]
+// mode 0: peek (result into st->peek_*), 1: advance the loop, 2: write candidate to cand[0..3].
+// all2 != 0: recompute every super-block maximum (after a full rebuild of the block maxima),
+// otherwise only the super-blocks the last refresh marked.  The last CTA to finish reduces the
+// super-block maxima and finalises.
 #define STBPE_SELECT_THREADS 256
-__global__ void __launch_bounds__(STBPE_SELECT_THREADS)
-    select_kernel(EngineDev e, int mode, Slot *partial, i64 *cand) {
-    DevState *st = e.st;
-    if (mode == 1 && st->stopped) return;
-    __shared__ u64 s_k[STBPE_SELECT_THREADS / 32];
-    __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
-    __shared__ int s_last;
-    u64 bk = STBPE_EMPTY;
-    i64 bc = 0;
-    for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < e.n_blocks;
-         i += gridDim.x * blockDim.x) {
-        const uint4 raw = *reinterpret_cast<const uint4 *>(e.blockmax + i);
-        const u64 k = ((u64)raw.y << 32) | raw.x;
-        const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
-        if (c > 0 && better(k, c, bk, bc)) {
-            bk = k;
-            bc = c;
-        }
-    }
+__device__ __forceinline__ void block_best(u64 &bk, i64 &bc, u64 *s_k, i64 *s_c) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
@@ -211,26 +198,56 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
         s_c[warp] = bc;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0)
         for (int w = 1; w < STBPE_SELECT_THREADS / 32; ++w)
             if (better(s_k[w], s_c[w], bk, bc)) {
                 bk = s_k[w];
                 bc = s_c[w];
             }
-        Slot s;
-        s.key = bk;
-        s.count = bc;
-        partial[blockIdx.x] = s;
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(STBPE_SELECT_THREADS)
+    select_kernel(EngineDev e, int mode, int all2, i64 *cand) {
+    DevState *st = e.st;
+    if (mode == 1 && st->stopped) return;
+    __shared__ u64 s_k[STBPE_SELECT_THREADS / 32];
+    __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
+    __shared__ int s_last;
+    const unsigned int n2 = all2 ? e.n_super2 : min(st->n_dirty2, e.n_super2);
+    for (unsigned int i = blockIdx.x; i < n2; i += gridDim.x) {
+        const unsigned int sb = all2 ? i : e.dirty2_list[i];
+        const unsigned int blk = sb * 256u + threadIdx.x;
+        u64 bk = STBPE_EMPTY;
+        i64 bc = 0;
+        if (blk < e.n_blocks) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(e.blockmax + blk);
+            const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
+            if (c > 0) {
+                bk = ((u64)raw.y << 32) | raw.x;
+                bc = c;
+            }
+        }
+        block_best(bk, bc, s_k, s_c);
+        if (threadIdx.x == 0) {
+            Slot s;
+            s.key = bk;
+            s.count = bc;
+            e.supermax[sb] = s;
+            e.dirty2_flag[sb] = 0u;
+        }
+    }
+    if (threadIdx.x == 0) {
         __threadfence();
         s_last = (atomicAdd(&st->ticket, 1u) == gridDim.x - 1);
     }
     __syncthreads();
-    if (!s_last || threadIdx.x != 0) return;
+    if (!s_last) return;
     __threadfence();
-    bk = STBPE_EMPTY;
-    bc = 0;
-    for (unsigned int i = 0; i < gridDim.x; ++i) {
-        const volatile Slot *p = partial + i;
+    u64 bk = STBPE_EMPTY;
+    i64 bc = 0;
+    for (unsigned int i = threadIdx.x; i < e.n_super2; i += STBPE_SELECT_THREADS) {
+        const volatile Slot *p = e.supermax + i;
         const u64 k = p->key;
         const i64 c = p->count;
         if (c > 0 && better(k, c, bk, bc)) {
@@ -238,7 +255,10 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
             bc = c;
         }
     }
+    block_best(bk, bc, s_k, s_c);
+    if (threadIdx.x != 0) return;
     st->ticket = 0;
+    st->n_dirty2 = 0;
     if (mode == 0) {
         st->peek_key = bk;
         st->peek_count = bc;
@@ -311,6 +331,20 @@ __global__ void export_stream_kernel(EngineDev e, const i64 *__restrict__ tile_o
         const int len = (int)(tile_off[tile + 1] - tile_off[tile]);
         const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
         for (int i = threadIdx.x; i < len; i += blockDim.x) out[tile_off[tile] + i] = (int32_t)g[i];
+    }
+}
+
+// Re-pack: tiles only ever shrink, so after many merges they are sparsely filled and the per-tile
+// cost of the pipeline is spread over few tokens.  The live tokens of all tiles are copied, in
+// order, into a dense stream (tile_off = exclusive prefix of the tile lengths).
+__global__ void repack_copy_kernel(EngineDev e, const i64 *__restrict__ tile_off, uint32_t *__restrict__ dst) {
+    const int warps_per_block = blockDim.x >> 5, lane = threadIdx.x & 31;
+    for (long long tile = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); tile < e.n_tiles;
+         tile += (long long)gridDim.x * warps_per_block) {
+        const i64 o = tile_off[tile];
+        const int len = (int)(tile_off[tile + 1] - o);
+        const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
+        for (int i = lane; i < len; i += 32) dst[o + i] = g[i];
     }
 }
 

@@ -108,7 +108,9 @@ class EngineWorker:
             self._check(self._lib.stbpe_mg_commit(self.e._h, self.all_cands.data_ptr(), self._s))
 
     def progress(self) -> Tuple[int, int]:
-        """(merges done, stop reason); synchronises."""
+        """(merges done, stop reason); synchronises.  Also the point where this rank re-packs its
+        own tiles when they have become sparse (a purely local decision)."""
+        self.e.repack()
         st = self.e.state()
         if st.device_error:
             self.e.count_error()

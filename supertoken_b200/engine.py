@@ -126,9 +126,15 @@ class Engine:
 
     def train_timed(self, n_merges: int):
         """Like ``train`` but returns device milliseconds spent in (select, merge, refresh)."""
-        ms = (ctypes.c_float * 3)()
+        ms = (ctypes.c_float * 4)()
         self._check(self._lib.stbpe_train_timed(self._h, int(n_merges), ms, self._s))
-        return float(ms[0]), float(ms[1]), float(ms[2])
+        return float(ms[0]), float(ms[1]), float(ms[2]), float(ms[3])
+
+    def repack(self, force: bool = False) -> bool:
+        """Dense re-pack of the stream if at most half of the tile capacity is live (or forced)."""
+        did = ctypes.c_int(0)
+        self._check(self._lib.stbpe_repack(self._h, int(force), ctypes.byref(did), self._s))
+        return bool(did.value)
 
     def count_error(self):
         """Raise the exception that matches the device error bits, if any are set."""

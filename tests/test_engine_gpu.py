@@ -225,3 +225,31 @@ def test_errors():
     with pytest.raises(CapacityError, match="capacity exceeded"):
         e.count_initial()
     e.close()
+
+
+def test_repack_keeps_merges_stream_and_histogram():
+    # a two-letter alphabet shrinks fast: the automatic re-pack (live <= half of the tile capacity)
+    # must trigger inside train(), and a forced one must be transparent too
+    rng = np.random.default_rng(21)
+    rows = [rng.integers(0, 2, int(rng.integers(1000, 90000))).tolist() for _ in range(12)]
+    ids, off = O.flatten_rows(rows)
+    target = 600
+    om, oc, reason = O.train_flat(ids, off, 256, target, 1)
+    e = _engine_for(ids, off, 256, target)
+    tiles0 = e.state().n_tiles
+    e.train(7)
+    assert e.repack(force=True)
+    e.train(target)          # several graph batches -> automatic re-packs in between
+    st = e.state()
+    assert st.n_tiles < tiles0 // 2
+    m, cnt, _ = e.merges()
+    assert m == om and cnt.tolist() == oc
+    ids2, off2 = ids.copy(), off.copy()
+    for i, (a, b) in enumerate(om):
+        O.apply_merge_flat(ids2, off2, a, b, 256 + i)
+    gi, go = e.export_stream()
+    assert np.array_equal(gi, ids2[:off2[-1]]) and st.live_tokens == off2[-1]
+    ok, okc = O.count_pairs_flat(ids2[:off2[-1]].copy(), off2, 1)
+    k, c = _hist(e)
+    assert np.array_equal(k, ok) and np.array_equal(c, okc)
+    e.close()
