@@ -57,6 +57,8 @@ typedef struct stbpe_state {
     int64_t table_slots;
     uint32_t device_error;    /* raw device error bits (0 = none) */
     int32_t n_tiles;
+    int64_t fixups;           /* dropped partners handled outside the visited tiles (statistics) */
+    int64_t repacks;          /* dense re-packs of the stream so far */
 } stbpe_state;
 
 /* Lifetime.  Replaces GPUBPETrainer's per-fit device contexts and workspaces

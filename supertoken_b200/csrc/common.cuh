@@ -27,6 +27,8 @@
 #define STBPE_IDMASK 0x7FFFFFFFu
 #define STBPE_EMPTY 0xFFFFFFFFFFFFFFFFull
 #define STBPE_BLK 256
+#define STBPE_PROWS 2048  // rows of the presence filter: token ids are hashed onto them
+#define STBPE_PROW_SHIFT 21  // 32 - log2(STBPE_PROWS)
 #define STBPE_MAX_PROBE (1u << 20)
 
 // device error bits
@@ -72,6 +74,10 @@ struct DevState {
     i64 export_n;
     unsigned int n_dirty2;     // super-blocks whose maximum must be recomputed
     unsigned int pad1;
+    int n_work;                // tiles on this merge's worklist; < 0 = every tile
+    int any_empty;             // some tile has become empty since the last re-pack
+    unsigned int n_fixups;     // partners dropped in a tile the merge did not visit (statistics)
+    int pad2;
     int exchange_only;         // multi-GPU: deltas still in flight, the next round only exchanges
     int round_incomplete;      // multi-GPU: this rank saw a full chunk or kept entries this round
 };
@@ -86,6 +92,13 @@ struct EngineDev {
     unsigned int *dirty_flag;
     unsigned int *dirty_list;
     unsigned int n_blocks;
+    // presence[r][w]: bit t of word w of row r says "a token whose id hashes to r may occur in tile
+    // 32*w + t" (set when such a token is written there, never cleared until the next re-pack).
+    // A Bloom-style filter with one hash: false positives cost a wasted visit, never a missed one.
+    unsigned int *presence;
+    unsigned int presence_words;  // words per row
+    unsigned int *cand_bits;      // tiles the current merge must visit
+    unsigned int *worklist;
     Slot *supermax;             // best entry of every 256 blocks (second level of the arg-max)
     unsigned int *dirty2_flag;
     unsigned int *dirty2_list;
@@ -111,6 +124,10 @@ __device__ __forceinline__ u64 mix64(u64 x) {
     x *= 0xc4ceb9fe1a85ec53ULL;
     x ^= x >> 33;
     return x;
+}
+
+__device__ __forceinline__ unsigned int presence_row(uint32_t id) {
+    return (id * 2654435761u) >> STBPE_PROW_SHIFT;
 }
 
 __device__ __forceinline__ int owner_of(u64 key, int world) {
@@ -312,7 +329,8 @@ __device__ __forceinline__ int current_rec(const EngineDev &e, int tile, int m, 
 // Live tokens around a tile, in stream order: the last two live tokens before it and up to
 // three live tokens after it (STBPE_NONE where the stream ends).  Walks records only.
 __device__ __forceinline__ void gather_halo(const EngineDev &e, int tile, int m, uint32_t &prev,
-                                            uint32_t &prev2, uint32_t nxt[3]) {
+                                            uint32_t &prev2, uint32_t nxt[3], int &next_tile) {
+    next_tile = -1;
     prev = prev2 = STBPE_NONE;
     nxt[0] = nxt[1] = nxt[2] = STBPE_NONE;
     TileRec r;
@@ -337,6 +355,7 @@ __device__ __forceinline__ void gather_halo(const EngineDev &e, int tile, int m,
     for (int t = tile + 1; t < e.n_tiles && have < 3; ++t) {
         current_rec(e, t, m, r);
         int take = r.len < 3 ? r.len : 3;
+        if (take > 0 && next_tile < 0) next_tile = t;
         for (int i = 0; i < take && have < 3; ++i) nxt[have++] = r.head[i];
     }
 }

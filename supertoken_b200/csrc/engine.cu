@@ -177,7 +177,10 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     ALLOC(e->d.merge_counts, (size_t)cfg->max_merges + 1);
     ALLOC(e->d.live_before, (size_t)cfg->max_merges + 1);
     ALLOC(e->partial, 4096);
-    ALLOC(e->cand, 2);
+    e->d.presence_words = (unsigned int)(((size_t)e->max_tiles + 31) / 32);
+    ALLOC(e->d.presence, (size_t)STBPE_PROWS * e->d.presence_words);
+    ALLOC(e->d.cand_bits, e->d.presence_words + 1);
+    ALLOC(e->d.worklist, (size_t)e->max_tiles + 32);
     if (cfg->world_size > 1) {
         e->lslots = 1ull << 22;
         e->d.lmask = e->lslots - 1;
@@ -335,9 +338,30 @@ static int prepare_stream_state(stbpe_engine *e, cudaStream_t s) {
     return STBPE_OK;
 }
 
+__global__ void clear_skip_state_kernel(EngineDev e) {
+    e.st->any_empty = 0;
+    e.st->n_work = -1;
+}
+
+// presence bitmaps follow the tile layout: rebuilt after a load and after every re-pack
+static int rebuild_presence(stbpe_engine *e, cudaStream_t s) {
+    clear_skip_state_kernel<<<1, 1, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    if (e->d.n_tiles > 0) {
+        presence_rebuild_kernel<<<e->sm_count * 2, 1024, 0, s>>>(e->d);
+        CK(cudaGetLastError());
+    }
+    return STBPE_OK;
+}
+
 static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
+    const bool fresh = e->recs_stale;
     int rc = prepare_stream_state(e, s);
     if (rc != STBPE_OK) return rc;
+    if (fresh) {
+        rc = rebuild_presence(e, s);
+        if (rc != STBPE_OK) return rc;
+    }
     clear_table_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
     CK(cudaMemsetAsync(e->d.dirty_flag, 0, e->d.n_blocks * sizeof(unsigned int), s));
@@ -406,6 +430,12 @@ STBPE_VISIBLE int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *cou
 
 static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s) {
     if (e->d.n_tiles > 0) {
+        worklist_reset_kernel<<<1, 1, 0, s>>>(e->d);
+        const int wl_words = (e->d.n_tiles + 31) / 32;
+        int wl_grid = (wl_words + 1023) / 1024;
+        if (wl_grid > 32) wl_grid = 32;
+        worklist_kernel<<<wl_grid, 1024, 0, s>>>(e->d);
+        CK(cudaGetLastError());
         int grid = e->merge_grid < e->d.n_tiles ? e->merge_grid : e->d.n_tiles;
         if (mg)
             merge_kernel<true><<<grid, STBPE_CTA_THREADS, e->merge_smem, s>>>(e->d, e->merge_slots);
@@ -480,6 +510,10 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
     if (e->d.n_tiles > 0) {
         init_recs_kernel<<<(e->d.n_tiles + 255) / 256, 256, 0, s>>>(e->d, total);
         CK(cudaGetLastError());
+    }
+    {
+        int rc = rebuild_presence(e, s);
+        if (rc != STBPE_OK) return rc;
     }
     CK(cudaStreamSynchronize(s));
     e->repacks++;
@@ -661,6 +695,8 @@ STBPE_VISIBLE int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *strea
     out->table_slots = (i64)e->slots;
     out->device_error = h.error;
     out->n_tiles = e->d.n_tiles;
+    out->fixups = h.n_fixups;
+    out->repacks = e->repacks;
     return STBPE_OK;
 }
 

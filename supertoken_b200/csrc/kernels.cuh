@@ -272,6 +272,86 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Tile skipping.  A merge (a,b) can only change a tile that holds a match head (a followed by b) or
+// the tile right after one (whose first token is the dropped b).  A head needs `a` in the tile and
+// `b` in the same or the next non-empty tile, so
+//     visit tile t  iff  present_a[t] and (present_b[t] or present_b[t+1])
+// (while some tile is empty "the next tile" may be further away and only present_a is used).
+// A dropped b in a tile that is not visited is removed by the warp that owns the head (fix-up in
+// the merge kernel).  This kernel builds the bitmap of visited tiles and the compact worklist.
+// ---------------------------------------------------------------------------------------
+__global__ void worklist_reset_kernel(EngineDev e) {
+    if (e.st->stopped || e.st->exchange_only) return;
+    e.st->n_work = 0;
+}
+
+__global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
+    DevState *st = e.st;
+    if (st->stopped || st->exchange_only) return;
+    const unsigned int *rowa = e.presence + (size_t)presence_row((uint32_t)st->cur_a) * e.presence_words;
+    const unsigned int *rowb =
+        st->any_empty ? nullptr : e.presence + (size_t)presence_row((uint32_t)st->cur_b) * e.presence_words;
+    const int n_words = (e.n_tiles + 31) / 32;
+    const int lane = threadIdx.x & 31;
+    for (int w0 = blockIdx.x * blockDim.x; w0 < n_words; w0 += gridDim.x * blockDim.x) {
+        const int w = w0 + threadIdx.x;
+        unsigned int c = 0;
+        if (w < n_words) {
+            c = rowa[w];
+            if (rowb) {
+                const unsigned int b0 = rowb[w];
+                const unsigned int b1 = (w + 1 < n_words) ? rowb[w + 1] : 0u;
+                c &= b0 | (b0 >> 1) | (b1 << 31);
+            }
+            const int rem = e.n_tiles - w * 32;
+            if (rem < 32) c &= (1u << rem) - 1u;
+            e.cand_bits[w] = c;
+        }
+        // warp-aggregated append of the set bits
+        const int cnt = __popc(c);
+        int incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int n = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += n;
+        }
+        const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+        int base = 0;
+        if (lane == 31 && total) base = atomicAdd(&st->n_work, total);
+        base = __shfl_sync(0xFFFFFFFFu, base, 31) + incl - cnt;
+        while (c) {
+            const int bit = __ffs(c) - 1;
+            c &= c - 1;
+            e.worklist[base++] = (unsigned int)(w * 32 + bit);
+        }
+    }
+}
+
+// (Re)build the presence filter from the stream: after a load and after every re-pack.  One CTA
+// handles 32 consecutive tiles, i.e. one word of every row: it collects the bits in shared memory
+// and then writes the STBPE_PROWS words with plain stores.
+__global__ void __launch_bounds__(1024) presence_rebuild_kernel(EngineDev e) {
+    __shared__ unsigned int s_rows[STBPE_PROWS];
+    const int n_groups = (e.n_tiles + 31) / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
+        for (int i = threadIdx.x; i < STBPE_PROWS; i += blockDim.x) s_rows[i] = 0u;
+        __syncthreads();
+        const int tile = grp * 32 + warp;  // blockDim.x == 1024: one warp per tile of the group
+        if (tile < e.n_tiles) {
+            TileRec r;
+            current_rec(e, tile, 0x7FFFFFFF, r);
+            const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
+            for (int i = lane; i < r.len; i += 32) atomicOr(&s_rows[presence_row(g[i] & STBPE_IDMASK)], 1u << warp);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < STBPE_PROWS; i += blockDim.x)
+            e.presence[(size_t)i * e.presence_words + grp] = s_rows[i];
+        __syncthreads();
+    }
+}
+
 // number of keys that hold exactly `count` (tie statistics; full table scan, on demand only)
 __global__ void count_ties_kernel(EngineDev e) {
     const i64 target = e.st->peek_count;

@@ -40,6 +40,8 @@ struct StageMeta {
     uint32_t prev;
     uint32_t nxt[3];
     uint32_t prev2;
+    int next_tile;  // tile that holds nxt[0] (-1: none)
+    int pad[3];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -133,23 +135,30 @@ __device__ __forceinline__ void pipe_setup(TilePipe &pipe) {
     __syncthreads();
 }
 
-// Producer warp: feeds this CTA's tiles (blockIdx.x, +gridDim.x, ...) through the ring, then one
-// end marker per consumer warp.
-__device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe, int m, int lane) {
+// Producer warp: feeds this CTA's tiles through the ring, then one end marker per consumer warp.
+// n_work < 0: tiles blockIdx.x, +gridDim.x, ...; otherwise the tiles listed in worklist items
+// blockIdx.x, +gridDim.x, ...
+__device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe, int m, int lane, int n_work) {
     unsigned int *derr = &e.st->error;
     const unsigned int lt = (1u << lane) - 1u;
     int it_base = 0;
     bool alive = true;
-    for (long long first = blockIdx.x; alive && first < e.n_tiles; first += 32ll * gridDim.x) {
-        const long long tl = first + (long long)lane * gridDim.x;
-        const int tile = tl < e.n_tiles ? (int)tl : -1;
+    for (long long j0 = 0; alive; j0 += 32) {
+        int tile = -1;
+        bool more;  // does the sequence continue past this batch?
+        const long long first = blockIdx.x + j0 * gridDim.x;
+        const long long limit = n_work < 0 ? (long long)e.n_tiles : (long long)n_work;
+        if (first >= limit) break;
+        const long long mine = first + (long long)lane * gridDim.x;
+        if (mine < limit) tile = n_work < 0 ? (int)mine : (int)e.worklist[mine];
+        more = first + 32ll * gridDim.x < limit;
         TileRec rec;
-        int slot = 0, len = 0;
+        int slot = 0, len = 0, next_tile = -1;
         uint32_t prev = STBPE_NONE, prev2 = STBPE_NONE, nxt[3] = {STBPE_NONE, STBPE_NONE, STBPE_NONE};
         if (tile >= 0) {
             slot = current_rec(e, tile, m, rec);
             len = rec.len;
-            if (len > 0) gather_halo(e, tile, m, prev, prev2, nxt);
+            if (len > 0) gather_halo(e, tile, m, prev, prev2, nxt, next_tile);
         }
         const unsigned int has = __ballot_sync(0xFFFFFFFFu, len > 0);
         const int my_it = it_base + __popc(has & lt);
@@ -170,6 +179,7 @@ __device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe
                     mt->nxt[0] = nxt[0];
                     mt->nxt[1] = nxt[1];
                     mt->nxt[2] = nxt[2];
+                    mt->next_tile = next_tile;
                     const uint32_t bytes = ((uint32_t)len * 4u + 15u) & ~15u;
                     mbar_arrive_expect_tx(&pipe.full[stage], bytes);
                     tma_load_1d(pipe.tok(stage), e.tiles + (i64)tile * STBPE_TILE, bytes, &pipe.full[stage]);
@@ -178,6 +188,7 @@ __device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe
             alive = __all_sync(0xFFFFFFFFu, ok) && alive;
         }
         it_base += __popc(has);
+        if (!more) break;
     }
     if (alive && lane < STBPE_NCW) {  // end markers: the next NCW iterations, one per consumer warp
         const int my_it = it_base + lane;
@@ -211,7 +222,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) count_kernel(EngineDev e
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m = 0x7FFFFFFF;  // every record version counts as "before"
     if (warp == STBPE_NCW) {
-        produce_tiles(e, pipe, m, lane);
+        produce_tiles(e, pipe, m, lane, -1);
     } else {
         unsigned int *derr = &e.st->error;
         for (int it = warp;; it += STBPE_NCW) {
@@ -297,6 +308,45 @@ __device__ __forceinline__ void merge_delta_terms(const SmemTable &tab, const En
     }
 }
 
+// Remove the first live token of a tile that this merge does not otherwise visit: it is the b of
+// a match whose head is the last token of the preceding tile.  One warp shifts the tile left by one
+// token in global memory (chunk by chunk: all reads of a chunk, then its writes) and writes the
+// tile's next record.  Nobody else touches this tile during the merge.
+__device__ __forceinline__ void drop_first_token(const EngineDev &e, int tile, int m, int lane) {
+    TileRec r;
+    const int slot = current_rec(e, tile, m, r);
+    uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
+    const int newlen = r.len - 1;
+    for (int c = 0; c < newlen; c += 128) {
+        uint32_t v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int q = c + lane * 4 + k;
+            v[k] = q < newlen ? g[q + 1] : 0u;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int q = c + lane * 4 + k;
+            if (q < newlen) g[q] = v[k];
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        TileRec *dst = &e.recs[2 * tile + (slot ^ 1)];
+        dst->len = newlen;
+        dst->head[0] = newlen > 0 ? r.head[1] : STBPE_NONE;
+        dst->head[1] = newlen > 1 ? r.head[2] : STBPE_NONE;
+        dst->head[2] = newlen > 2 ? g[2] : STBPE_NONE;
+        dst->tail = newlen > 0 ? r.tail : STBPE_NONE;
+        dst->tail2 = newlen > 1 ? r.tail2 : STBPE_NONE;
+        dst->ver = m;
+        if (newlen == 0) e.st->any_empty = 1;
+        atomicAdd(&e.st->n_fixups, 1u);
+    }
+    __syncwarp();
+}
+
 // Match windows are queued per warp and their delta terms are added 32 at a time, one window
 // per lane: a table add is a dependent chain of a few hundred cycles, which a single lane
 // walking its own matches one after the other would pay in full for every term.
@@ -324,8 +374,9 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
     pipe.carve(smem_raw, smem_slots);
     pipe_setup(pipe);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_work = st->n_work;  // < 0: every tile
     if (warp == STBPE_NCW) {
-        produce_tiles(e, pipe, m, lane);
+        produce_tiles(e, pipe, m, lane, n_work);
     } else {
         unsigned int *derr = &st->error;
         i64 removed = 0, matches = 0;
@@ -348,6 +399,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
             const int len = mp->len;
             int base = 0;          // tokens written so far (compacted in place)
             bool changed = false;  // warp-uniform
+            bool any_head = false, last_head = false;  // warp-uniform
             // does the first token of the next chunk vanish (its left neighbour heads a match)?
             bool carry_drop = ((mp->prev & STBPE_IDMASK) == a) && (s_tok[0] == b);
             uint32_t pw4 = mp->prev2, pw5 = mp->prev;  // this lane's tokens 2,3 of the previous chunk (pre-merge)
@@ -433,6 +485,13 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                     }
                 }
                 changed = true;  // a head or a carried drop: the tile is rewritten
+                {
+                    const unsigned int hb = __ballot_sync(0xFFFFFFFFu, heads != 0u);
+                    any_head |= hb != 0u;
+                    const int lastq = len - 1 - cq;  // position of the tile's last token in this chunk
+                    if (lastq >= 0 && lastq < STBPE_CHUNK)
+                        last_head = (__shfl_sync(0xFFFFFFFFu, heads, lastq >> 2) >> (lastq & 3)) & 1u;
+                }
                 // the last position of the chunk heads a match: its partner opens the next chunk
                 carry_drop = ((__ballot_sync(0xFFFFFFFFu, (heads >> 3) & 1u) >> 31) & 1u) && whole;
                 const int cnt = __popc(keep);
@@ -458,6 +517,19 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
             const int newlen = base;
             if (!(STBPE_DBG & 8)) fence_async_smem();  // the bulk store reads these writes through the async proxy
             __syncwarp();
+            if (any_head && lane == 0) {  // the new token now occurs in this tile
+                unsigned int *p = e.presence + (size_t)presence_row(nw) * e.presence_words + ((unsigned int)tile >> 5);
+                if (!(*(volatile unsigned int *)p & (1u << (tile & 31)))) atomicOr(p, 1u << (tile & 31));
+            }
+            if (last_head && n_work >= 0 && mp->next_tile >= 0) {
+                // the dropped partner opens the next non-empty tile; if this merge does not visit
+                // that tile, drop it here
+                const unsigned int su = (unsigned int)mp->next_tile;
+                if (!((e.cand_bits[su >> 5] >> (su & 31)) & 1u)) {
+                    drop_first_token(e, mp->next_tile, m, lane);
+                    if (lane == 0) removed += 1;
+                }
+            }
             if (lane == 0) {
                 if (newlen > 0 && !(STBPE_DBG & 1)) {
                     tma_store_1d(e.tiles + (i64)tile * STBPE_TILE, s_tok, ((uint32_t)newlen * 4u + 15u) & ~15u);
@@ -473,6 +545,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                 dst->tail2 = newlen > 1 ? s_tok[newlen - 2] : STBPE_NONE;
                 dst->ver = m;
                 removed += len - newlen;
+                if (newlen == 0) st->any_empty = 1;
                 if (newlen == 0 || (STBPE_DBG & 1)) mbar_arrive(&pipe.empty[stage]);
             }
         }

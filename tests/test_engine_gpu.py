@@ -253,3 +253,38 @@ def test_repack_keeps_merges_stream_and_histogram():
     k, c = _hist(e)
     assert np.array_equal(k, ok) and np.array_equal(c, okc)
     e.close()
+
+
+def test_tile_skipping_fixup_for_matches_that_straddle_tiles():
+    # A merge visits only the tiles whose presence filter admits a (and b in the same or the next
+    # tile).  Here every 300 is the last token of its tile and its 301 partner opens the next tile,
+    # which holds no 300: the warp that owns the head has to drop the partner in the unvisited tile.
+    T = 1024
+    rng = np.random.default_rng(4)
+    ids = rng.integers(0, 5, 40 * T + 100).astype(np.int32)
+    for t in (3, 4, 17, 30):                 # tiles 3|4|5 chain, 17|18, 30|31
+        ids[(t + 1) * T - 1], ids[(t + 1) * T] = 300, 301
+    ids[9 * T + 50], ids[9 * T + 51] = 301, 300      # (301, 300): not a match
+    ids[31 * T + 1:32 * T] = 4
+    off = np.array([0, 10, 12 * T + 7, len(ids)], dtype=np.int64)
+    e = _engine_for(ids, off, 256, 60)
+    assert e.apply_merge(300, 301, 256) == 4   # id 256 = base_vocab + 0, as the loop numbers merges
+    assert e.state().fixups >= 2             # tiles 18 and 31 hold no 300 (5 does: it is visited)
+    ids2, off2 = ids.copy(), off.copy()
+    assert O.apply_merge_flat(ids2, off2, 300, 301, 256) == 4
+    gi, go = e.export_stream()
+    assert np.array_equal(gi, ids2[:off2[-1]]) and np.array_equal(go, off2)
+    ok, okc = O.count_pairs_flat(ids2[:off2[-1]].copy(), off2, 1)
+    k, c = _hist(e)
+    assert np.array_equal(k, ok) and np.array_equal(c, okc)
+    # keep training: later merges see the rewritten tiles and records
+    e.train(40)
+    m, cnt, _ = e.merges()
+    om, oc, _ = O.train_flat(ids2[:off2[-1]].copy(), off2, 257, 40, 1)
+    assert m[1:] == om and cnt.tolist()[1:] == oc
+    e.close()
+
+
+def test_long_training_with_skipping_and_repacks_matches_oracle():
+    c = synth.config2_mixed(3 << 20, seed=8, lexicon=3000, mean_doc_bytes=900)
+    _check_against_oracle([r for r in corpus_rows(c)], 256, 700)
