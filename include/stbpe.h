@@ -59,6 +59,7 @@ typedef struct stbpe_state {
     int32_t n_tiles;
     int64_t fixups;           /* dropped partners handled outside the visited tiles (statistics) */
     int64_t repacks;          /* dense re-packs of the stream so far */
+    int64_t work_tiles;       /* tiles visited by the last merge (after the presence filter) */
 } stbpe_state;
 
 /* Lifetime.  Replaces GPUBPETrainer's per-fit device contexts and workspaces

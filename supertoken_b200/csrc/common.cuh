@@ -27,8 +27,7 @@
 #define STBPE_IDMASK 0x7FFFFFFFu
 #define STBPE_EMPTY 0xFFFFFFFFFFFFFFFFull
 #define STBPE_BLK 256
-#define STBPE_PROWS 2048  // rows of the presence filter: token ids are hashed onto them
-#define STBPE_PROW_SHIFT 21  // 32 - log2(STBPE_PROWS)
+#define STBPE_PROWS 8192  // rows of the pair filter: pair keys are hashed onto them (two hashes)
 #define STBPE_MAX_PROBE (1u << 20)
 
 // device error bits
@@ -75,7 +74,7 @@ struct DevState {
     unsigned int n_dirty2;     // super-blocks whose maximum must be recomputed
     unsigned int pad1;
     int n_work;                // tiles on this merge's worklist; < 0 = every tile
-    int any_empty;             // some tile has become empty since the last re-pack
+    int filter_stale;          // (unused) visit every tile
     unsigned int n_fixups;     // partners dropped in a tile the merge did not visit (statistics)
     int pad2;
     int exchange_only;         // multi-GPU: deltas still in flight, the next round only exchanges
@@ -92,9 +91,12 @@ struct EngineDev {
     unsigned int *dirty_flag;
     unsigned int *dirty_list;
     unsigned int n_blocks;
-    // presence[r][w]: bit t of word w of row r says "a token whose id hashes to r may occur in tile
-    // 32*w + t" (set when such a token is written there, never cleared until the next re-pack).
-    // A Bloom-style filter with one hash: false positives cost a wasted visit, never a missed one.
+    // presence[r][w]: bit t of word w of row r says "a pair whose key hashes to r may start in tile
+    // 32*w + t" (the tile of the pair's left token; set when such a pair comes into being, never
+    // cleared until the next re-pack).  A Bloom filter with two hashes per pair: false positives
+    // cost a wasted visit, never a missed one.  Row STBPE_PROWS is a wildcard: tiles that every
+    // merge visits because the pair that starts at their last token is not known exactly (their
+    // last token is the result of a run of equal tokens that ran on into the next tile).
     unsigned int *presence;
     unsigned int presence_words;  // words per row
     unsigned int *cand_bits;      // tiles the current merge must visit
@@ -126,9 +128,6 @@ __device__ __forceinline__ u64 mix64(u64 x) {
     return x;
 }
 
-__device__ __forceinline__ unsigned int presence_row(uint32_t id) {
-    return (id * 2654435761u) >> STBPE_PROW_SHIFT;
-}
 
 __device__ __forceinline__ int owner_of(u64 key, int world) {
     return (int)((mix64(key) >> 40) % (u64)world);
@@ -254,6 +253,23 @@ __device__ __forceinline__ unsigned int hash32(u64 key) {
     return h;
 }
 
+// pair filter: the two rows of a pair key, and setting the pair's bits for a tile
+__device__ __forceinline__ void filter_rows(u64 key, unsigned int &r1, unsigned int &r2) {
+    const unsigned int h = hash32(key);
+    r1 = h & (STBPE_PROWS - 1);
+    r2 = (h >> 16) & (STBPE_PROWS - 1);
+}
+__device__ __forceinline__ void filter_set(const EngineDev &e, int tile, u64 key) {
+    if (tile < 0) return;
+    unsigned int r1, r2;
+    filter_rows(key, r1, r2);
+    const unsigned int w = (unsigned int)tile >> 5, bit = 1u << (tile & 31);
+    unsigned int *p1 = e.presence + (size_t)r1 * e.presence_words + w;
+    unsigned int *p2 = e.presence + (size_t)r2 * e.presence_words + w;
+    if (!(*(volatile unsigned int *)p1 & bit)) atomicOr(p1, bit);
+    if (!(*(volatile unsigned int *)p2 & bit)) atomicOr(p2, bit);
+}
+
 // slow path: probe for the key, claim an empty slot, or give up after a few probes
 template <bool MG>
 __device__ __noinline__ void smem_table_add_probe(SmemTable t, const EngineDev *e, u64 key, int delta,
@@ -329,8 +345,8 @@ __device__ __forceinline__ int current_rec(const EngineDev &e, int tile, int m, 
 // Live tokens around a tile, in stream order: the last two live tokens before it and up to
 // three live tokens after it (STBPE_NONE where the stream ends).  Walks records only.
 __device__ __forceinline__ void gather_halo(const EngineDev &e, int tile, int m, uint32_t &prev,
-                                            uint32_t &prev2, uint32_t nxt[3], int &next_tile) {
-    next_tile = -1;
+                                            uint32_t &prev2, uint32_t nxt[3], int &next_tile, int &prev_tile) {
+    next_tile = prev_tile = -1;
     prev = prev2 = STBPE_NONE;
     nxt[0] = nxt[1] = nxt[2] = STBPE_NONE;
     TileRec r;
@@ -340,6 +356,7 @@ __device__ __forceinline__ void gather_halo(const EngineDev &e, int tile, int m,
         if (r.len > 0) {
             if (back == 0) {
                 prev = r.tail;
+                prev_tile = t;
                 back = 1;
                 if (r.len > 1) {
                     prev2 = r.tail2;

@@ -178,7 +178,7 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     ALLOC(e->d.live_before, (size_t)cfg->max_merges + 1);
     ALLOC(e->partial, 4096);
     e->d.presence_words = (unsigned int)(((size_t)e->max_tiles + 31) / 32);
-    ALLOC(e->d.presence, (size_t)STBPE_PROWS * e->d.presence_words);
+    ALLOC(e->d.presence, (size_t)(STBPE_PROWS + 1) * e->d.presence_words);
     ALLOC(e->d.cand_bits, e->d.presence_words + 1);
     ALLOC(e->d.worklist, (size_t)e->max_tiles + 32);
     if (cfg->world_size > 1) {
@@ -339,7 +339,7 @@ static int prepare_stream_state(stbpe_engine *e, cudaStream_t s) {
 }
 
 __global__ void clear_skip_state_kernel(EngineDev e) {
-    e.st->any_empty = 0;
+    e.st->filter_stale = 0;
     e.st->n_work = -1;
 }
 
@@ -697,6 +697,7 @@ STBPE_VISIBLE int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *strea
     out->n_tiles = e->d.n_tiles;
     out->fixups = h.n_fixups;
     out->repacks = e->repacks;
+    out->work_tiles = h.n_work;
     return STBPE_OK;
 }
 

@@ -273,37 +273,34 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
 }
 
 // ---------------------------------------------------------------------------------------
-// Tile skipping.  A merge (a,b) can only change a tile that holds a match head (a followed by b) or
-// the tile right after one (whose first token is the dropped b).  A head needs `a` in the tile and
-// `b` in the same or the next non-empty tile, so
-//     visit tile t  iff  present_a[t] and (present_b[t] or present_b[t+1])
-// (while some tile is empty "the next tile" may be further away and only present_a is used).
-// A dropped b in a tile that is not visited is removed by the warp that owns the head (fix-up in
-// the merge kernel).  This kernel builds the bitmap of visited tiles and the compact worklist.
+// Tile skipping.  A merge (a,b) changes a tile only if a match head sits in it (the pair (a,b)
+// starts there) or if its first token is the partner of a head that ends the tile before it.  The
+// pair filter records, per tile, which pairs start in it (including the pair formed by its last
+// token and the first token of the next non-empty tile), so
+//     visit tile t  iff  filter row1(a,b)[t] and filter row2(a,b)[t].
+// A partner in a tile that is not visited is dropped by the warp that owns the head (fix-up in the
+// merge kernel).  This kernel builds the bitmap of visited tiles and the compact worklist.
 // ---------------------------------------------------------------------------------------
 __global__ void worklist_reset_kernel(EngineDev e) {
     if (e.st->stopped || e.st->exchange_only) return;
-    e.st->n_work = 0;
+    e.st->n_work = e.st->filter_stale ? -1 : 0;
 }
 
 __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
     DevState *st = e.st;
-    if (st->stopped || st->exchange_only) return;
-    const unsigned int *rowa = e.presence + (size_t)presence_row((uint32_t)st->cur_a) * e.presence_words;
-    const unsigned int *rowb =
-        st->any_empty ? nullptr : e.presence + (size_t)presence_row((uint32_t)st->cur_b) * e.presence_words;
+    if (st->stopped || st->exchange_only || st->filter_stale) return;
+    unsigned int r1, r2;
+    filter_rows(((u64)(uint32_t)st->cur_a << 32) | (u64)(uint32_t)st->cur_b, r1, r2);
+    const unsigned int *row1 = e.presence + (size_t)r1 * e.presence_words;
+    const unsigned int *row2 = e.presence + (size_t)r2 * e.presence_words;
+    const unsigned int *wild = e.presence + (size_t)STBPE_PROWS * e.presence_words;
     const int n_words = (e.n_tiles + 31) / 32;
     const int lane = threadIdx.x & 31;
     for (int w0 = blockIdx.x * blockDim.x; w0 < n_words; w0 += gridDim.x * blockDim.x) {
         const int w = w0 + threadIdx.x;
         unsigned int c = 0;
         if (w < n_words) {
-            c = rowa[w];
-            if (rowb) {
-                const unsigned int b0 = rowb[w];
-                const unsigned int b1 = (w + 1 < n_words) ? rowb[w + 1] : 0u;
-                c &= b0 | (b0 >> 1) | (b1 << 31);
-            }
+            c = (row1[w] & row2[w]) | wild[w];
             const int rem = e.n_tiles - w * 32;
             if (rem < 32) c &= (1u << rem) - 1u;
             e.cand_bits[w] = c;
@@ -328,9 +325,9 @@ __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
     }
 }
 
-// (Re)build the presence filter from the stream: after a load and after every re-pack.  One CTA
-// handles 32 consecutive tiles, i.e. one word of every row: it collects the bits in shared memory
-// and then writes the STBPE_PROWS words with plain stores.
+// (Re)build the pair filter from the stream: after a load and after every re-pack.  One CTA handles
+// 32 consecutive tiles, i.e. one word of every row: it collects the bits in shared memory and then
+// writes the STBPE_PROWS words with plain stores.
 __global__ void __launch_bounds__(1024) presence_rebuild_kernel(EngineDev e) {
     __shared__ unsigned int s_rows[STBPE_PROWS];
     const int n_groups = (e.n_tiles + 31) / 32;
@@ -342,12 +339,31 @@ __global__ void __launch_bounds__(1024) presence_rebuild_kernel(EngineDev e) {
         if (tile < e.n_tiles) {
             TileRec r;
             current_rec(e, tile, 0x7FFFFFFF, r);
-            const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
-            for (int i = lane; i < r.len; i += 32) atomicOr(&s_rows[presence_row(g[i] & STBPE_IDMASK)], 1u << warp);
+            if (r.len > 0) {
+                const uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;
+                uint32_t nxt0 = STBPE_NONE;  // first live token after the tile
+                for (int t = tile + 1; t < e.n_tiles; ++t) {
+                    TileRec rn;
+                    current_rec(e, t, 0x7FFFFFFF, rn);
+                    if (rn.len > 0) {
+                        nxt0 = rn.head[0];
+                        break;
+                    }
+                }
+                for (int i = lane; i < r.len; i += 32) {
+                    const uint32_t t1 = (i + 1 < r.len) ? g[i + 1] : nxt0;
+                    if (t1 & STBPE_FLAG) continue;  // not a countable pair
+                    unsigned int r1, r2;
+                    filter_rows(((u64)(g[i] & STBPE_IDMASK) << 32) | (u64)t1, r1, r2);
+                    atomicOr(&s_rows[r1], 1u << warp);
+                    atomicOr(&s_rows[r2], 1u << warp);
+                }
+            }
         }
         __syncthreads();
         for (int i = threadIdx.x; i < STBPE_PROWS; i += blockDim.x)
             e.presence[(size_t)i * e.presence_words + grp] = s_rows[i];
+        if (threadIdx.x == 0) e.presence[(size_t)STBPE_PROWS * e.presence_words + grp] = 0u;  // no wildcards
         __syncthreads();
     }
 }

@@ -32,6 +32,7 @@ static_assert(STBPE_NS % STBPE_NCW == 0 && STBPE_NS >= 16, "ring size must be a 
 #define STBPE_CTA_THREADS ((STBPE_NCW + 1) * 32)  // + producer warp
 #define STBPE_CHUNK 128                          // tokens per warp step (4 per lane)
 #define STBPE_QCAP 64                            // per-warp queue of match windows awaiting their delta terms
+#define STBPE_QWORDS 8                           // words per queued window: 6 tokens, tile of the token before the head, own tile
 
 struct StageMeta {
     int tile;  // -1 = end of the sequence for the consumer warp that receives it
@@ -41,7 +42,8 @@ struct StageMeta {
     uint32_t nxt[3];
     uint32_t prev2;
     int next_tile;  // tile that holds nxt[0] (-1: none)
-    int pad[3];
+    int prev_tile;  // tile that holds prev (-1: none)
+    int pad[2];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -97,7 +99,7 @@ struct TilePipe {
     StageMeta *meta;
     uint64_t *full;
     uint64_t *empty;
-    uint32_t *queue;  // STBPE_NCW queues of STBPE_QCAP windows of 6 tokens (merge kernel)
+    uint32_t *queue;  // STBPE_NCW queues of STBPE_QCAP windows of STBPE_QWORDS words (merge kernel)
     SmemTable tab;
 
     __device__ __forceinline__ void carve(unsigned char *base, unsigned int table_slots) {
@@ -119,7 +121,7 @@ struct TilePipe {
     static size_t bytes(unsigned int table_slots) {
         return (size_t)STBPE_NS * STBPE_TILE * sizeof(uint32_t) + (size_t)table_slots * 12 +
                2 * STBPE_NS * sizeof(uint64_t) + STBPE_NS * sizeof(StageMeta) +
-               (size_t)STBPE_NCW * STBPE_QCAP * 6 * sizeof(uint32_t) + 16;
+               (size_t)STBPE_NCW * STBPE_QCAP * STBPE_QWORDS * sizeof(uint32_t) + 16;
     }
 };
 
@@ -153,12 +155,12 @@ __device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe
         if (mine < limit) tile = n_work < 0 ? (int)mine : (int)e.worklist[mine];
         more = first + 32ll * gridDim.x < limit;
         TileRec rec;
-        int slot = 0, len = 0, next_tile = -1;
+        int slot = 0, len = 0, next_tile = -1, prev_tile = -1;
         uint32_t prev = STBPE_NONE, prev2 = STBPE_NONE, nxt[3] = {STBPE_NONE, STBPE_NONE, STBPE_NONE};
         if (tile >= 0) {
             slot = current_rec(e, tile, m, rec);
             len = rec.len;
-            if (len > 0) gather_halo(e, tile, m, prev, prev2, nxt, next_tile);
+            if (len > 0) gather_halo(e, tile, m, prev, prev2, nxt, next_tile, prev_tile);
         }
         const unsigned int has = __ballot_sync(0xFFFFFFFFu, len > 0);
         const int my_it = it_base + __popc(has & lt);
@@ -180,6 +182,7 @@ __device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe
                     mt->nxt[1] = nxt[1];
                     mt->nxt[2] = nxt[2];
                     mt->next_tile = next_tile;
+                    mt->prev_tile = prev_tile;
                     const uint32_t bytes = ((uint32_t)len * 4u + 15u) & ~15u;
                     mbar_arrive_expect_tx(&pipe.full[stage], bytes);
                     tma_load_1d(pipe.tok(stage), e.tiles + (i64)tile * STBPE_TILE, bytes, &pipe.full[stage]);
@@ -275,23 +278,30 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) count_kernel(EngineDev e
 // ---------------------------------------------------------------------------------------
 template <bool MG>
 __device__ __forceinline__ void merge_delta_terms(const SmemTable &tab, const EngineDev &e, uint32_t a, uint32_t b,
-                                               uint32_t nw, uint32_t tm2, uint32_t tm1, uint32_t t0, uint32_t t1,
-                                               uint32_t t2, uint32_t t3) {
+                                                  uint32_t nw, uint32_t tm2, uint32_t tm1, uint32_t t0, uint32_t t1,
+                                                  uint32_t t2, uint32_t t3, int tile_x, int tile_own) {
+    // every pair that comes into being (+1 term) is also entered into the pair filter of the tile
+    // that holds its left token: tile_x for the token before the head, tile_own for the head
     if (a != b) {
         if (!(t0 & STBPE_FLAG)) {
             const bool x_dropped = (tm1 == b) && ((tm2 & STBPE_IDMASK) == a);
             if (x_dropped) {
-                smem_table_add<MG>(tab, e, ((u64)nw << 32) | (u64)nw, 1);
+                const u64 k = ((u64)nw << 32) | (u64)nw;
+                smem_table_add<MG>(tab, e, k, 1);
+                filter_set(e, tile_x, k);  // the preceding head became `new` where x's left neighbour was
             } else {
                 const u64 x = (u64)(tm1 & STBPE_IDMASK) << 32;
                 smem_table_add<MG>(tab, e, x | (u64)a, -1);
                 smem_table_add<MG>(tab, e, x | (u64)nw, 1);
+                filter_set(e, tile_x, x | (u64)nw);
             }
         }
         if (!(t2 & STBPE_FLAG)) {
             smem_table_add<MG>(tab, e, ((u64)b << 32) | (u64)t2, -1);
             const bool M2 = (t2 == a) && (t3 == b);
-            if (!M2) smem_table_add<MG>(tab, e, ((u64)nw << 32) | (u64)t2, 1);
+            const u64 k = ((u64)nw << 32) | (u64)(M2 ? nw : t2);
+            if (!M2) smem_table_add<MG>(tab, e, k, 1);
+            filter_set(e, tile_own, k);
         }
     } else {
         const bool head = ((t0 & STBPE_IDMASK) == a) && (t1 == b);
@@ -300,10 +310,14 @@ __device__ __forceinline__ void merge_delta_terms(const SmemTable &tab, const En
                 const u64 x = (u64)(tm1 & STBPE_IDMASK) << 32;
                 smem_table_add<MG>(tab, e, x | (u64)a, -1);
                 smem_table_add<MG>(tab, e, x | (u64)nw, 1);
+                filter_set(e, tile_x, x | (u64)nw);
             }
         } else if (!(t1 & STBPE_FLAG)) {
             smem_table_add<MG>(tab, e, ((u64)a << 32) | (u64)t1, -1);
-            smem_table_add<MG>(tab, e, ((u64)nw << 32) | (u64)t1, 1);
+            const u64 k = ((u64)nw << 32) | (u64)t1;
+            smem_table_add<MG>(tab, e, k, 1);
+            filter_set(e, tile_own, k);  // right when the run started in this tile; the tile where a
+                                          // run that crosses tiles started is a wildcard instead
         }
     }
 }
@@ -341,7 +355,6 @@ __device__ __forceinline__ void drop_first_token(const EngineDev &e, int tile, i
         dst->tail = newlen > 0 ? r.tail : STBPE_NONE;
         dst->tail2 = newlen > 1 ? r.tail2 : STBPE_NONE;
         dst->ver = m;
-        if (newlen == 0) e.st->any_empty = 1;
         atomicAdd(&e.st->n_fixups, 1u);
     }
     __syncwarp();
@@ -355,8 +368,8 @@ __device__ __forceinline__ void drain_queue(const SmemTable &tab, const EngineDe
                                             uint32_t nw, const uint32_t *q, int n, int lane) {
     __syncwarp();
     for (int i = lane; i < n; i += 32) {
-        const uint32_t *d = q + i * 6;
-        merge_delta_terms<MG>(tab, e, a, b, nw, d[0], d[1], d[2], d[3], d[4], d[5]);
+        const uint32_t *d = q + i * STBPE_QWORDS;
+        merge_delta_terms<MG>(tab, e, a, b, nw, d[0], d[1], d[2], d[3], d[4], d[5], (int)d[6], (int)d[7]);
     }
     __syncwarp();
 }
@@ -381,7 +394,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
         unsigned int *derr = &st->error;
         i64 removed = 0, matches = 0;
         int pending = -1;  // lane 0: stage whose bulk store may still be reading shared memory
-        uint32_t *queue = pipe.queue + (size_t)warp * STBPE_QCAP * 6;
+        uint32_t *queue = pipe.queue + (size_t)warp * STBPE_QCAP * STBPE_QWORDS;
         int qn = 0;  // warp-uniform
         const unsigned int lt = (1u << lane) - 1u;
         for (int it = warp;; it += STBPE_NCW) {
@@ -474,8 +487,10 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                     const unsigned int om = __ballot_sync(0xFFFFFFFFu, owns);
                     if (om) {
                         if (owns) {
-                            uint32_t *d = queue + (qn + __popc(om & lt)) * 6;
+                            uint32_t *d = queue + (qn + __popc(om & lt)) * STBPE_QWORDS;
                             d[0] = w[k], d[1] = w[1 + k], d[2] = w[2 + k], d[3] = w[3 + k], d[4] = w[4 + k], d[5] = w[5 + k];
+                            d[6] = (uint32_t)((q0 + k) > 0 ? tile : mp->prev_tile);
+                            d[7] = (uint32_t)tile;
                         }
                         qn += __popc(om);
                         if (qn >= 32) {
@@ -517,9 +532,11 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
             const int newlen = base;
             if (!(STBPE_DBG & 8)) fence_async_smem();  // the bulk store reads these writes through the async proxy
             __syncwarp();
-            if (any_head && lane == 0) {  // the new token now occurs in this tile
-                unsigned int *p = e.presence + (size_t)presence_row(nw) * e.presence_words + ((unsigned int)tile >> 5);
-                if (!(*(volatile unsigned int *)p & (1u << (tile & 31)))) atomicOr(p, 1u << (tile & 31));
+            if (same && last_head && lane == 0) {
+                // the run of a's goes on in the next tile: the pair that will start at the collapsed
+                // token is decided by whoever finds the run's tail, so visit this tile from now on
+                unsigned int *p = e.presence + (size_t)STBPE_PROWS * e.presence_words + ((unsigned int)tile >> 5);
+                atomicOr(p, 1u << (tile & 31));
             }
             if (last_head && n_work >= 0 && mp->next_tile >= 0) {
                 // the dropped partner opens the next non-empty tile; if this merge does not visit
@@ -527,7 +544,17 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                 const unsigned int su = (unsigned int)mp->next_tile;
                 if (!((e.cand_bits[su >> 5] >> (su & 31)) & 1u)) {
                     drop_first_token(e, mp->next_tile, m, lane);
-                    if (lane == 0) removed += 1;
+                    if (lane == 0) {
+                        removed += 1;
+                        // a == b: the dropped token is the tail of the run and would have owned the
+                        // terms of the pair behind the run; its tile is not visited, so add them here
+                        const uint32_t y = mp->nxt[1];
+                        if (same && !(y & STBPE_FLAG)) {
+                            smem_table_add<MG>(pipe.tab, e, ((u64)a << 32) | (u64)y, -1);
+                            smem_table_add<MG>(pipe.tab, e, ((u64)nw << 32) | (u64)y, 1);
+                            filter_set(e, tile, ((u64)nw << 32) | (u64)y);
+                        }
+                    }
                 }
             }
             if (lane == 0) {
@@ -545,7 +572,6 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                 dst->tail2 = newlen > 1 ? s_tok[newlen - 2] : STBPE_NONE;
                 dst->ver = m;
                 removed += len - newlen;
-                if (newlen == 0) st->any_empty = 1;
                 if (newlen == 0 || (STBPE_DBG & 1)) mbar_arrive(&pipe.empty[stage]);
             }
         }

@@ -288,3 +288,31 @@ def test_tile_skipping_fixup_for_matches_that_straddle_tiles():
 def test_long_training_with_skipping_and_repacks_matches_oracle():
     c = synth.config2_mixed(3 << 20, seed=8, lexicon=3000, mean_doc_bytes=900)
     _check_against_oracle([r for r in corpus_rows(c)], 256, 700)
+
+
+def test_equal_pair_runs_that_end_in_an_unvisited_tile():
+    # a == b with the run's tail as the first token of a tile that holds no other (a, a) pair:
+    # the head's owner drops the tail there and must also account for the pair behind the run
+    T = 1024
+    rng = np.random.default_rng(6)
+    ids = rng.integers(0, 4, 24 * T).astype(np.int32)
+    ids[ids == 3] = 2
+    for t in (2, 9, 10, 15):
+        ids[(t + 1) * T - 3:(t + 1) * T + 2] = [1, 0, 7, 7, 1]   # ... 7 | 7 1 ...: run of two across the seam
+    ids[20 * T - 2:20 * T + 3] = [7, 7, 7, 7, 0]                 # run of four across a seam
+    off = np.array([0, 5 * T + 3, len(ids)], dtype=np.int64)
+    _check_against_oracle([ids[off[i]:off[i + 1]].tolist() for i in range(2)], 256, 30)
+    e = _engine_for(ids, off, 256, 30)
+    assert e.apply_merge(7, 7, 256) > 0
+    ids2, off2 = ids.copy(), off.copy()
+    O.apply_merge_flat(ids2, off2, 7, 7, 256)
+    ok, okc = O.count_pairs_flat(ids2[:off2[-1]].copy(), off2, 1)
+    k, c = _hist(e)
+    assert np.array_equal(k, ok) and np.array_equal(c, okc)
+    gi, _ = e.export_stream()
+    assert np.array_equal(gi, ids2[:off2[-1]])
+    e.train(25)
+    om, oc, _ = O.train_flat(ids2[:off2[-1]].copy(), off2, 257, 25, 1)
+    m, cnt, _ = e.merges()
+    assert m[1:] == om and cnt.tolist()[1:] == oc
+    e.close()
