@@ -59,7 +59,8 @@ typedef struct stbpe_state {
     int32_t n_tiles;
     int64_t fixups;           /* dropped partners handled outside the visited tiles (statistics) */
     int64_t repacks;          /* dense re-packs of the stream so far */
-    int64_t work_tiles;       /* tiles visited by the last merge (after the presence filter) */
+    int64_t work_tiles;       /* tiles visited by the last merge (after the pair filter) */
+    double count_kernel_ms;   /* device time of the histogram kernel(s) of the last count */
 } stbpe_state;
 
 /* Lifetime.  Replaces GPUBPETrainer's per-fit device contexts and workspaces

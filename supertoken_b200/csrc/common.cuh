@@ -36,6 +36,7 @@
 #define STBPE_DERR_LTABLE_FULL 4u
 #define STBPE_DERR_KEY_MISSING 8u
 #define STBPE_DERR_BAD_ID 16u
+#define STBPE_DERR_DENSE_OVERFLOW 64u
 
 typedef unsigned long long u64;
 typedef long long i64;

@@ -28,6 +28,10 @@ struct stbpe_engine {
     unsigned int merge_slots, count_slots;
     size_t merge_smem, count_smem;
     bool recs_stale, counted;
+    u64 *dense;           // 65 536 global counters of the byte-level count path
+    bool only_bytes;      // every token so far came from stbpe_append_bytes (ids < 256)
+    float count_ms;       // device time of the histogram kernels of the last count
+    cudaEvent_t ev0, ev1;
     uint32_t *tiles_alt;  // second stream buffer, allocated at the first re-pack
     int repacks;
     cudaGraphExec_t graph;
@@ -100,6 +104,8 @@ STBPE_VISIBLE int stbpe_destroy(stbpe_engine *e) {
     if (!e) return STBPE_OK;
     cudaSetDevice(e->cfg.device);
     if (e->graph) cudaGraphExecDestroy(e->graph);
+    if (e->ev0) cudaEventDestroy(e->ev0);
+    if (e->ev1) cudaEventDestroy(e->ev1);
     for (void *p : e->allocs) cudaFree(p);
     delete e;
     return STBPE_OK;
@@ -115,6 +121,7 @@ static int reset_state(stbpe_engine *e, cudaStream_t s) {
     e->d.n_tiles = 0;
     e->recs_stale = true;
     e->counted = false;
+    e->only_bytes = true;
     return STBPE_OK;
 }
 
@@ -131,6 +138,8 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->graph_merges = 0;
     e->tiles_alt = nullptr;
     e->repacks = 0;
+    e->count_ms = 0.f;
+    e->ev0 = e->ev1 = nullptr;
     e->use_graph = getenv("STBPE_NO_GRAPH") == nullptr;
     memset(&e->d, 0, sizeof(e->d));
     auto bail = [&](int code) {
@@ -177,6 +186,7 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     ALLOC(e->d.merge_counts, (size_t)cfg->max_merges + 1);
     ALLOC(e->d.live_before, (size_t)cfg->max_merges + 1);
     ALLOC(e->partial, 4096);
+    ALLOC(e->dense, 65536);
     e->d.presence_words = (unsigned int)(((size_t)e->max_tiles + 31) / 32);
     ALLOC(e->d.presence, (size_t)(STBPE_PROWS + 1) * e->d.presence_words);
     ALLOC(e->d.cand_bits, e->d.presence_words + 1);
@@ -288,6 +298,7 @@ static int append_common(stbpe_engine *e, const void *data, i64 n, size_t elem, 
     e->n_tokens += n;
     e->recs_stale = true;
     e->counted = false;
+    if (elem != 1) e->only_bytes = false;
     return STBPE_OK;
 }
 
@@ -371,13 +382,47 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
     CK(cudaMemsetAsync(&e->d.st->n_dirty, 0, sizeof(unsigned int), s));
     CK(cudaMemsetAsync(&e->d.st->n_dirty2, 0, sizeof(unsigned int), s));
     CK(cudaMemsetAsync(&e->d.st->n_keys, 0, sizeof(u64), s));
+    if (!e->ev0) {
+        CK(cudaEventCreate(&e->ev0));
+        CK(cudaEventCreate(&e->ev1));
+    }
+    if (e->d.n_tiles > 0 && fresh && e->only_bytes && !getenv("STBPE_NO_DENSE_COUNT")) {
+        // byte-level fast path: dense stream, ids < 256
+        CK(cudaMemsetAsync(e->dense, 0, 65536 * sizeof(u64), s));
+        CK(cudaEventRecord(e->ev0, s));
+        CK(cudaFuncSetAttribute(count_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
+        count_dense_kernel<<<e->sm_count, STBPE_DENSE_THREADS, 32768 * 4, s>>>(e->d, e->n_tokens, e->dense);
+        CK(cudaGetLastError());
+        unsigned int derr = 0;
+        CK(cudaMemcpyAsync(&derr, &e->d.st->error, sizeof(derr), cudaMemcpyDeviceToHost, s));
+        CK(cudaStreamSynchronize(s));
+        if (!(derr & STBPE_DERR_DENSE_OVERFLOW)) {
+            if (mg)
+                dense_to_table_kernel<true><<<256, 256, 0, s>>>(e->d, e->dense);
+            else
+                dense_to_table_kernel<false><<<256, 256, 0, s>>>(e->d, e->dense);
+            CK(cudaGetLastError());
+            CK(cudaEventRecord(e->ev1, s));
+            CK(cudaEventSynchronize(e->ev1));
+            CK(cudaEventElapsedTime(&e->count_ms, e->ev0, e->ev1));
+            return STBPE_OK;
+        }
+        // a 16-bit counter came too close to its limit: discard and count with the general kernel
+        derr &= ~STBPE_DERR_DENSE_OVERFLOW;
+        CK(cudaMemcpyAsync(&e->d.st->error, &derr, sizeof(derr), cudaMemcpyHostToDevice, s));
+        CK(cudaStreamSynchronize(s));
+    }
     if (e->d.n_tiles > 0) {
         int grid = e->count_grid < e->d.n_tiles ? e->count_grid : e->d.n_tiles;
+        CK(cudaEventRecord(e->ev0, s));
         if (mg)
             count_kernel<true><<<grid, STBPE_CTA_THREADS, e->count_smem, s>>>(e->d, e->count_slots);
         else
             count_kernel<false><<<grid, STBPE_CTA_THREADS, e->count_smem, s>>>(e->d, e->count_slots);
         CK(cudaGetLastError());
+        CK(cudaEventRecord(e->ev1, s));
+        CK(cudaEventSynchronize(e->ev1));
+        CK(cudaEventElapsedTime(&e->count_ms, e->ev0, e->ev1));
     }
     return STBPE_OK;
 }
@@ -698,6 +743,7 @@ STBPE_VISIBLE int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *strea
     out->fixups = h.n_fixups;
     out->repacks = e->repacks;
     out->work_tiles = h.n_work;
+    out->count_kernel_ms = e->count_ms;
     return STBPE_OK;
 }
 

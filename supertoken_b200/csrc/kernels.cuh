@@ -78,6 +78,91 @@ __global__ void clear_table_kernel(EngineDev e) {
 #include "tile_kernels.cuh"
 
 // ---------------------------------------------------------------------------------------
+// K2, byte-level fast path.  Right after a load of bytes the stream is dense (every tile full)
+// and every id is below 256, so a pair key fits 16 bits and the whole histogram fits a CTA's
+// shared memory as 65 536 16-bit counters (two per 32-bit word, 128 KB).  Each token costs one
+// shared-memory atomic on a direct index: no hashing, no key compare.
+// A 16-bit counter is kept below 2^15: the thread whose add takes it to 0x8000 moves 0x8000 of it
+// to the global 64-bit counter.  Should a counter ever be seen at 0xC000 or above (32 768 further
+// adds would have to slip in before that subtraction lands) the kernel raises
+// STBPE_DERR_DENSE_OVERFLOW and the host recounts with the general kernel, so the result is exact
+// or the failure is reported, never silently wrong.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void dense_add(unsigned int *s_tab, u64 *g_dense, unsigned int *derr, uint32_t t0,
+                                          uint32_t t1) {
+    if (t1 & STBPE_FLAG) return;  // the right token starts a row (or lies past the end)
+    const unsigned int key = ((t0 & 0xFFu) << 8) | t1;
+    const unsigned int sh = (key & 1u) * 16u;
+    const unsigned int old = atomicAdd(&s_tab[key >> 1], 1u << sh);
+    const unsigned int h = (old >> sh) & 0xFFFFu;
+    if (h >= 0x7FFFu) {  // rare
+        if (h == 0x7FFFu) {
+            atomicSub(&s_tab[key >> 1], 0x8000u << sh);
+            atomicAdd(&g_dense[key], 0x8000ull);
+        } else if (h >= 0xC000u) {
+            atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
+        }
+    }
+}
+
+#define STBPE_DENSE_THREADS 1024
+#define STBPE_DENSE_UNROLL 4
+__global__ void __launch_bounds__(STBPE_DENSE_THREADS, 1)
+    count_dense_kernel(EngineDev e, i64 n_tokens, u64 *g_dense) {
+    extern __shared__ __align__(16) unsigned int s_tab[];  // 32 768 words
+    for (int i = threadIdx.x; i < 32768; i += STBPE_DENSE_THREADS) s_tab[i] = 0u;
+    __syncthreads();
+    const uint32_t *tok = e.tiles;
+    unsigned int *derr = &e.st->error;
+    const int lane = threadIdx.x & 31;
+    const i64 span = (i64)STBPE_DENSE_THREADS * 4;  // tokens per CTA step
+    for (i64 base = (i64)blockIdx.x * span * STBPE_DENSE_UNROLL; base < n_tokens;
+         base += (i64)gridDim.x * span * STBPE_DENSE_UNROLL) {
+        uint4 v[STBPE_DENSE_UNROLL];
+        uint32_t nx[STBPE_DENSE_UNROLL];
+#pragma unroll
+        for (int u = 0; u < STBPE_DENSE_UNROLL; ++u) {  // all loads first: several in flight per thread
+            const i64 i = base + u * span + (i64)threadIdx.x * 4;
+            if (i + 4 <= n_tokens) {
+                v[u] = *reinterpret_cast<const uint4 *>(tok + i);
+            } else {
+                v[u].x = i < n_tokens ? tok[i] : STBPE_NONE;
+                v[u].y = i + 1 < n_tokens ? tok[i + 1] : STBPE_NONE;
+                v[u].z = i + 2 < n_tokens ? tok[i + 2] : STBPE_NONE;
+                v[u].w = i + 3 < n_tokens ? tok[i + 3] : STBPE_NONE;
+            }
+            nx[u] = (lane == 31) ? (i + 4 < n_tokens ? tok[i + 4] : STBPE_NONE) : 0u;
+        }
+        // tokens past the end were loaded as STBPE_NONE: as a right-hand token NONE carries the
+        // row-start flag (no pair), and a left-hand NONE is always followed by another NONE
+#pragma unroll
+        for (int u = 0; u < STBPE_DENSE_UNROLL; ++u) {
+            uint32_t n0 = __shfl_down_sync(0xFFFFFFFFu, v[u].x, 1);
+            if (lane == 31) n0 = nx[u];
+            dense_add(s_tab, g_dense, derr, v[u].x, v[u].y);
+            dense_add(s_tab, g_dense, derr, v[u].y, v[u].z);
+            dense_add(s_tab, g_dense, derr, v[u].z, v[u].w);
+            dense_add(s_tab, g_dense, derr, v[u].w, n0);
+        }
+    }
+    __syncthreads();
+    for (int w = threadIdx.x; w < 32768; w += STBPE_DENSE_THREADS) {
+        const unsigned int x = s_tab[w];
+        if (x & 0xFFFFu) atomicAdd(&g_dense[2 * w], (u64)(x & 0xFFFFu));
+        if (x >> 16) atomicAdd(&g_dense[2 * w + 1], (u64)(x >> 16));
+    }
+}
+
+// dense 16-bit keys -> entries of the pair table (or of the rank-local delta table)
+template <bool MG>
+__global__ void dense_to_table_kernel(EngineDev e, const u64 *g_dense) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= 65536) return;
+    const u64 c = g_dense[k];
+    if (c) sink_add<MG>(e, ((u64)(k >> 8) << 32) | (u64)(k & 0xFF), (i64)c);
+}
+
+// ---------------------------------------------------------------------------------------
 // K4  arg-max: block maxima refresh + reduction with the reference's tie-break
 // ---------------------------------------------------------------------------------------
 __global__ void refresh_kernel(EngineDev e, int all) {

@@ -316,3 +316,33 @@ def test_equal_pair_runs_that_end_in_an_unvisited_tile():
     m, cnt, _ = e.merges()
     assert m[1:] == om and cnt.tolist()[1:] == oc
     e.close()
+
+
+@pytest.mark.parametrize("kind", ["equal", "random", "two_rows_short", "text"])
+def test_byte_level_dense_count_path(kind):
+    # append_bytes + first count takes the dense 16-bit-counter kernel; one hot pair far beyond
+    # 2^15 occurrences exercises the counter hand-over to the 64-bit totals
+    rng = np.random.default_rng(2)
+    if kind == "equal":
+        data = np.full(700_001, 97, np.uint8)
+        off = np.array([0, 300_000, 300_000, 700_001], dtype=np.int64)
+    elif kind == "random":
+        data = rng.integers(0, 256, (1 << 20) + 3).astype(np.uint8)
+        off = np.sort(np.concatenate([[0, len(data)], rng.choice(len(data), 200, replace=False)])).astype(np.int64)
+    elif kind == "two_rows_short":
+        data = np.array([1, 2, 1, 2, 1], np.uint8)
+        off = np.array([0, 3, 5], dtype=np.int64)
+    else:
+        c = synth.config2_mixed(1 << 20, seed=12, lexicon=2000, mean_doc_bytes=500)
+        data, off = np.asarray(c.data), np.asarray(c.row_offsets)
+    e = Engine(len(data), max_merges=8, table_slots=1 << 18)
+    e.append_bytes(data, off)
+    e.count_initial()
+    ok, oc = O.count_pairs_flat(data.astype(np.int32), np.unique(off) if kind == "random" else off, 1)
+    k, c = _hist(e)
+    assert np.array_equal(k, ok) and np.array_equal(c, oc)
+    e.train(8)
+    om, ocnt, _ = O.train_flat(data.astype(np.int32), off, 256, 8, 1)
+    m, cnt, _ = e.merges()
+    assert m == om and cnt.tolist() == ocnt
+    e.close()
