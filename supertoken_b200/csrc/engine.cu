@@ -3,6 +3,7 @@
 #include <cub/device/device_scan.cuh>
 #include <cuda_runtime.h>
 
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -526,6 +527,9 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
     CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
     if (!force && (h.n_live * 4 > (i64)nt * STBPE_TILE * 3 || nt < 64)) return STBPE_OK;  // re-pack at <= 75 % fill
+    const bool dbg = getenv("STBPE_DEBUG_TIMING") != nullptr;
+    auto now = [&]() { cudaStreamSynchronize(s); return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); };
+    double t_a = dbg ? now() : 0;
     if (!e->tiles_alt) CK(dev_alloc(e, &e->tiles_alt, (size_t)e->max_tiles * STBPE_TILE));
     i64 *lens = nullptr, *offs = nullptr;
     CK(cudaMallocAsync((void **)&lens, (size_t)(nt + 1) * sizeof(i64), s));
@@ -539,8 +543,10 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
     CK(cudaMallocAsync(&tmp, tmp_bytes ? tmp_bytes : 16, s));
     cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, lens, offs, nt + 1, s);
     CK(cudaGetLastError());
+    double t_b = dbg ? now() : 0;
     repack_copy_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, offs, e->tiles_alt);
     CK(cudaGetLastError());
+    double t_c = dbg ? now() : 0;
     i64 total = 0;
     CK(cudaMemcpyAsync(&total, offs + nt, sizeof(i64), cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
@@ -556,11 +562,13 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
         init_recs_kernel<<<(e->d.n_tiles + 255) / 256, 256, 0, s>>>(e->d, total);
         CK(cudaGetLastError());
     }
+    double t_d = dbg ? now() : 0;
     {
         int rc = rebuild_presence(e, s);
         if (rc != STBPE_OK) return rc;
     }
     CK(cudaStreamSynchronize(s));
+    if (dbg) fprintf(stderr, "[repack] scan %.2f copy %.2f recs %.2f filter %.2f ms (tiles %d -> %d)\n", t_b - t_a, t_c - t_b, t_d - t_c, now() - t_d, nt, e->d.n_tiles);
     e->repacks++;
     if (did) *did = 1;
     return STBPE_OK;

@@ -300,28 +300,45 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
     __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
     __shared__ int s_last;
     const unsigned int n2 = all2 ? e.n_super2 : min(st->n_dirty2, e.n_super2);
-    for (unsigned int i = blockIdx.x; i < n2; i += gridDim.x) {
-        const unsigned int sb = all2 ? i : e.dirty2_list[i];
-        const unsigned int blk = sb * 256u + threadIdx.x;
-        u64 bk = STBPE_EMPTY;
-        i64 bc = 0;
-        if (blk < e.n_blocks) {
-            const uint4 raw = *reinterpret_cast<const uint4 *>(e.blockmax + blk);
-            const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
-            if (c > 0) {
-                bk = ((u64)raw.y << 32) | raw.x;
-                bc = c;
+    {   // one warp per super-block: 256 block maxima, 8 per lane
+        const unsigned int lane = threadIdx.x & 31;
+        const unsigned int wpb = STBPE_SELECT_THREADS / 32;
+        for (unsigned int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < n2; i += gridDim.x * wpb) {
+            const unsigned int sb = all2 ? i : e.dirty2_list[i];
+            u64 bk = STBPE_EMPTY;
+            i64 bc = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const unsigned int blk = sb * 256u + j * 32u + lane;
+                if (blk < e.n_blocks) {
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(e.blockmax + blk);
+                    const u64 k = ((u64)raw.y << 32) | raw.x;
+                    const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
+                    if (c > 0 && better(k, c, bk, bc)) {
+                        bk = k;
+                        bc = c;
+                    }
+                }
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                const u64 ok = __shfl_down_sync(0xFFFFFFFFu, bk, d);
+                const i64 oc = __shfl_down_sync(0xFFFFFFFFu, bc, d);
+                if (better(ok, oc, bk, bc)) {
+                    bk = ok;
+                    bc = oc;
+                }
+            }
+            if (lane == 0) {
+                Slot s;
+                s.key = bk;
+                s.count = bc;
+                e.supermax[sb] = s;
+                e.dirty2_flag[sb] = 0u;
             }
         }
-        block_best(bk, bc, s_k, s_c);
-        if (threadIdx.x == 0) {
-            Slot s;
-            s.key = bk;
-            s.count = bc;
-            e.supermax[sb] = s;
-            e.dirty2_flag[sb] = 0u;
-        }
     }
+    __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         s_last = (atomicAdd(&st->ticket, 1u) == gridDim.x - 1);

@@ -21,6 +21,7 @@ waits for another), and (c) CPU stand-in workers over ``gloo`` (tests of the pro
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
