@@ -165,6 +165,21 @@ int stbpe_mg_apply_inbox(stbpe_engine *e, void *stream);
 int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev /* 4 x int64 */, void *stream);
 int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev /* world x 4 int64 */, void *stream);
 
+/* The same rounds issued natively on one stream, without a host call per step: the library
+ * resolves NCCL from the process at run time and keeps its own communicator.
+ *   stbpe_mg_nccl_unique_id : rank 0 obtains the 128-byte NCCL id, the caller broadcasts it
+ *   stbpe_mg_nccl_init      : every rank joins the communicator (and gets exchange buffers of
+ *                             cap_per_peer entries per peer if none were set).  The communicator is
+ *                             created once per process and device and reused by later engines of the
+ *                             same world size and rank (id128 is then ignored)
+ *   stbpe_mg_run            : enqueue n_rounds rounds (first != 0: round 0 is the local count); each
+ *                             round = local kernel, all-to-all of the chunks (grouped ncclSend/ncclRecv),
+ *                             owner insert, candidate, all-gather, commit.  Does not synchronise.
+ * Stand in for the NCCL process-group set-up of the reference (gpu_tokenizer/dist/launcher.py:143-182). */
+int stbpe_mg_nccl_unique_id(void *out128);
+int stbpe_mg_nccl_init(stbpe_engine *e, const void *id128, int64_t cap_per_peer);
+int stbpe_mg_run(stbpe_engine *e, int first, int n_rounds, void *stream);
+
 /* Stateless operators on padded [B, L] batches resident on the device, with the
  * reference's operator signatures.
  * stbpe_rows_count_pairs  <- utils.count_pairs (gpu_tokenizer/utils.py:691-706): unique

@@ -58,6 +58,9 @@ SIGNATURES = {
     "stbpe_mg_apply_inbox": (_int, [_vp, _vp]),
     "stbpe_mg_candidate": (_int, [_vp, _vp, _vp]),
     "stbpe_mg_commit": (_int, [_vp, _vp, _vp]),
+    "stbpe_mg_nccl_unique_id": (_int, [_vp]),
+    "stbpe_mg_nccl_init": (_int, [_vp, _vp, _i64]),
+    "stbpe_mg_run": (_int, [_vp, _int, _int, _vp]),
     "stbpe_rows_count_pairs": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
     "stbpe_rows_count_pairs_noalloc": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp,
                                               ctypes.c_char_p, ctypes.c_size_t]),

@@ -2,6 +2,8 @@
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
 
 #include <chrono>
 #include <cstdio>
@@ -31,6 +33,9 @@ struct stbpe_engine {
     bool recs_stale, counted;
     u64 *dense;           // 65 536 global counters of the byte-level count path
     bool only_bytes;      // every token so far came from stbpe_append_bytes (ids < 256)
+    ncclComm_t comm;      // own NCCL communicator for the native multi-GPU round loop
+    i64 *all_cands;       // world x 4 gathered candidates (native loop)
+    bool own_boxes;
     float count_ms;       // device time of the histogram kernels of the last count
     cudaEvent_t ev0, ev1;
     uint32_t *tiles_alt;  // second stream buffer, allocated at the first re-pack
@@ -45,6 +50,7 @@ struct stbpe_engine {
 };
 
 static thread_local std::string g_create_err;
+namespace { struct NcclApi; NcclApi &nccl_api(); void nccl_comm_destroy(void *comm); }
 
 static int fail(stbpe_engine *e, int code, const std::string &msg) {
     if (e)
@@ -105,6 +111,7 @@ STBPE_VISIBLE int stbpe_destroy(stbpe_engine *e) {
     if (!e) return STBPE_OK;
     cudaSetDevice(e->cfg.device);
     if (e->graph) cudaGraphExecDestroy(e->graph);
+    // the NCCL communicator is shared by the engines of this process and lives until exit
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
     for (void *p : e->allocs) cudaFree(p);
@@ -141,6 +148,9 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->repacks = 0;
     e->count_ms = 0.f;
     e->ev0 = e->ev1 = nullptr;
+    e->comm = nullptr;
+    e->all_cands = nullptr;
+    e->own_boxes = false;
     e->use_graph = getenv("STBPE_NO_GRAPH") == nullptr;
     memset(&e->d, 0, sizeof(e->d));
     auto bail = [&](int code) {
@@ -188,6 +198,8 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     ALLOC(e->d.live_before, (size_t)cfg->max_merges + 1);
     ALLOC(e->partial, 4096);
     ALLOC(e->dense, 65536);
+    ALLOC(e->cand, 4);
+    ALLOC(e->all_cands, (size_t)4 * cfg->world_size);
     e->d.presence_words = (unsigned int)(((size_t)e->max_tiles + 31) / 32);
     ALLOC(e->d.presence, (size_t)(STBPE_PROWS + 1) * e->d.presence_words);
     ALLOC(e->d.cand_bits, e->d.presence_words + 1);
@@ -929,6 +941,139 @@ STBPE_VISIBLE int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev, vo
     set_target_if_unset_kernel<<<1, 1, 0, s>>>(e->d, e->cfg.max_merges);
     commit_kernel<<<1, 1, 0, s>>>(e->d, (const i64 *)all_cands_dev);
     CK(cudaGetLastError());
+    return STBPE_OK;
+}
+
+// ------------------------------------------------------------------ native NCCL round loop
+// The rounds of the multi-GPU merge loop issued from C++ on one stream: kernels, an all-to-all of
+// the outbox chunks (grouped ncclSend/ncclRecv over NVLink) and an all-gather of the candidates,
+// with no Python and no host synchronisation per round.  NCCL is resolved at run time from the
+// library that is already loaded in the process (no link-time dependency).
+}  // extern "C"
+
+namespace {
+struct NcclApi {
+    bool ok = false;
+    decltype(&ncclGetUniqueId) GetUniqueId = nullptr;
+    decltype(&ncclCommInitRank) CommInitRank = nullptr;
+    decltype(&ncclCommDestroy) CommDestroy = nullptr;
+    decltype(&ncclGroupStart) GroupStart = nullptr;
+    decltype(&ncclGroupEnd) GroupEnd = nullptr;
+    decltype(&ncclSend) Send = nullptr;
+    decltype(&ncclRecv) Recv = nullptr;
+    decltype(&ncclAllGather) AllGather = nullptr;
+    decltype(&ncclGetErrorString) GetErrorString = nullptr;
+};
+NcclApi &nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (h) {
+#define NCCL_SYM(field, name) api.field = reinterpret_cast<decltype(api.field)>(dlsym(h, name))
+            NCCL_SYM(GetUniqueId, "ncclGetUniqueId");
+            NCCL_SYM(CommInitRank, "ncclCommInitRank");
+            NCCL_SYM(CommDestroy, "ncclCommDestroy");
+            NCCL_SYM(GroupStart, "ncclGroupStart");
+            NCCL_SYM(GroupEnd, "ncclGroupEnd");
+            NCCL_SYM(Send, "ncclSend");
+            NCCL_SYM(Recv, "ncclRecv");
+            NCCL_SYM(AllGather, "ncclAllGather");
+            NCCL_SYM(GetErrorString, "ncclGetErrorString");
+#undef NCCL_SYM
+            api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.GroupStart && api.GroupEnd &&
+                     api.Send && api.Recv && api.AllGather && api.GetErrorString;
+        }
+    }
+    return api;
+}
+void nccl_comm_destroy(void *comm) {
+    if (comm && nccl_api().ok) nccl_api().CommDestroy((ncclComm_t)comm);
+}
+}  // namespace
+
+extern "C" {
+
+#define NCK(call)                                                                              \
+    do {                                                                                       \
+        ncclResult_t r_ = (call);                                                              \
+        if (r_ != ncclSuccess) return fail(e, STBPE_E_CUDA, std::string(#call) + ": " + nccl_api().GetErrorString(r_)); \
+    } while (0)
+
+STBPE_VISIBLE int stbpe_mg_nccl_unique_id(void *out128) {
+    stbpe_engine *e = nullptr;
+    if (!out128) return STBPE_E_BADARG;
+    if (!nccl_api().ok) return fail(e, STBPE_E_STATE, "NCCL library not found in this process");
+    ncclUniqueId id;
+    NCK(nccl_api().GetUniqueId(&id));
+    memcpy(out128, &id, sizeof(id));
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_nccl_init(stbpe_engine *e, const void *id128, int64_t cap_per_peer) {
+    if (!e || !id128 || cap_per_peer < 1) return STBPE_E_BADARG;
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    if (!nccl_api().ok) return fail(e, STBPE_E_STATE, "NCCL library not found in this process");
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->own_boxes) {
+        cudaError_t c;
+        const size_t n = (size_t)e->cfg.world_size * (cap_per_peer + 1);
+        if ((c = dev_alloc(e, &e->d.outbox, n)) != cudaSuccess) return cuda_fail(e, c, "cudaMalloc outbox");
+        if ((c = dev_alloc(e, &e->d.inbox, n)) != cudaSuccess) return cuda_fail(e, c, "cudaMalloc inbox");
+        CK(cudaMemset(e->d.outbox, 0, n * sizeof(Slot)));
+        CK(cudaMemset(e->d.inbox, 0, n * sizeof(Slot)));
+        e->d.cap_per_peer = cap_per_peer;
+        e->own_boxes = true;
+    }
+    // one communicator per process and device, shared by every engine created later with the same
+    // world size and rank (setting one up costs far more than a training run of a small corpus)
+    static ncclComm_t g_comm[64] = {};
+    static int g_world[64] = {}, g_rank[64] = {};
+    const int dev = e->cfg.device;
+    if (dev >= 0 && dev < 64 && g_comm[dev] && g_world[dev] == e->cfg.world_size && g_rank[dev] == e->cfg.rank) {
+        e->comm = g_comm[dev];
+        return STBPE_OK;
+    }
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    NCK(nccl_api().CommInitRank(&e->comm, e->cfg.world_size, id, e->cfg.rank));
+    if (dev >= 0 && dev < 64) {
+        g_comm[dev] = e->comm;
+        g_world[dev] = e->cfg.world_size;
+        g_rank[dev] = e->cfg.rank;
+    }
+    return STBPE_OK;
+}
+
+// first != 0: round 0 counts the local rows; every other round applies the committed merge (or only
+// drains, in an exchange-only round).  n_rounds rounds are enqueued on the stream; no synchronisation.
+STBPE_VISIBLE int stbpe_mg_run(stbpe_engine *e, int first, int n_rounds, void *stream) {
+    if (!e || n_rounds < 0) return STBPE_E_BADARG;
+    if (!e->comm) return fail(e, STBPE_E_STATE, "call stbpe_mg_nccl_init first");
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    const NcclApi &api = nccl_api();
+    const int world = e->cfg.world_size;
+    const size_t chunk = (size_t)(e->d.cap_per_peer + 1) * sizeof(Slot);
+    for (int r = 0; r < n_rounds; ++r) {
+        int rc = (first && r == 0) ? stbpe_mg_count_local(e, stream) : stbpe_mg_merge_local(e, stream);
+        if (rc != STBPE_OK) return rc;
+        NCK(api.GroupStart());
+        for (int p = 0; p < world; ++p) {
+            NCK(api.Send((const char *)e->d.outbox + p * chunk, chunk, ncclChar, p, e->comm, s));
+            NCK(api.Recv((char *)e->d.inbox + p * chunk, chunk, ncclChar, p, e->comm, s));
+        }
+        NCK(api.GroupEnd());
+        rc = stbpe_mg_apply_inbox(e, stream);
+        if (rc != STBPE_OK) return rc;
+        rc = stbpe_mg_candidate(e, e->cand, stream);
+        if (rc != STBPE_OK) return rc;
+        NCK(api.AllGather(e->cand, e->all_cands, 4, ncclInt64, e->comm, s));
+        rc = stbpe_mg_commit(e, e->all_cands, stream);
+        if (rc != STBPE_OK) return rc;
+    }
     return STBPE_OK;
 }
 

@@ -195,6 +195,59 @@ class ShardedBPE:
             budget -= n
 
 
+class NativeLoop:
+    """The same rounds issued by the library itself (``stbpe_mg_run``): kernels, grouped
+    ncclSend/ncclRecv and ncclAllGather on one stream from C++, no Python and no host
+    synchronisation per round.  ``torch.distributed`` is used once, to hand the NCCL id to every
+    rank.  One engine (one GPU) per process."""
+
+    _joined = set()   # (device index, world, rank) whose communicator exists in this process
+
+    def __init__(self, engine, cap_per_peer: int = 4096, group=None):
+        import torch.distributed as dist
+        self.e = engine
+        self._lib = L.load()
+        key = (engine.device.index, engine.world_size, engine.rank)
+        raw = bytes(128)
+        if key not in NativeLoop._joined:
+            ident = torch.zeros(128, dtype=torch.uint8)
+            if dist.get_rank(group) == 0:
+                buf = (ctypes.c_ubyte * 128)()
+                engine._check(self._lib.stbpe_mg_nccl_unique_id(buf))
+                ident = torch.tensor(list(buf), dtype=torch.uint8)
+            ident = ident.to(engine.device)
+            dist.broadcast(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            raw = bytes(ident.cpu().tolist())
+            NativeLoop._joined.add(key)
+        with torch.cuda.device(engine.device):
+            engine._check(self._lib.stbpe_mg_nccl_init(engine._h, raw, int(cap_per_peer)))
+        self.rounds = 0
+        self._counted = False
+
+    def run(self, n_rounds: int):
+        first = 0 if self._counted else 1
+        with torch.cuda.device(self.e.device):
+            self.e._check(self._lib.stbpe_mg_run(self.e._h, first, int(n_rounds), self.e._s))
+        self._counted = True
+        self.rounds += n_rounds
+
+    def progress(self) -> Tuple[int, int]:
+        self.e.repack()
+        st = self.e.state()
+        if st.device_error:
+            self.e.count_error()
+        return int(st.merges_done), int(st.stop_reason)
+
+    def train(self, check_every: int = 256):
+        if not self._counted:
+            self.run(1)
+        while True:
+            done, reason = self.progress()
+            if reason != L.RUNNING:
+                return done, reason
+            self.run(check_every)
+
+
 # ----------------------------------------------------------------------------- bench (N > 1)
 def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     """``bench.py`` at N > 1: the same corpus as N = 1, rows sharded over the ranks (strong
@@ -220,10 +273,14 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     torch.cuda.empty_cache()
     n_local = int(shard.numel())
 
+    native = not os.environ.get("STBPE_MG_PYTHON_ROUNDS")
+
     def make(max_merges):
         e = Engine(max(n_local, 1), base_vocab=256, max_merges=max(max_merges, 1), device=dev,
                    world_size=world, rank=rank)
-        return e, EngineWorker(e, cap_per_peer=8192)
+        if native:
+            return e, NativeLoop(e, cap_per_peer=4096)
+        return e, ShardedBPE([EngineWorker(e, cap_per_peer=4096)], TorchDistComm())
 
     def ev():
         x = torch.cuda.Event(enable_timing=True)
@@ -236,20 +293,22 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
         return float(t.item())
 
     # warm-up on a throw-away engine
-    e, w = make(W)
+    e, loop = make(W)
     e.append_bytes(shard, shard_off)
-    ShardedBPE([w], TorchDistComm()).train(check_every=8)
+    loop.train(check_every=8)
     e.close()
-    del e, w
+    del e, loop
 
-    e, w = make(K)
+    e, loop = make(K)
     e.append_bytes(shard, shard_off)
-    loop = ShardedBPE([w], TorchDistComm())
     torch.cuda.synchronize()
     dist.barrier()
     t0 = ev()
-    loop._round(True)               # initial histogram + exchange + first decision
-    loop._counted = True
+    if native:                      # initial histogram + exchange + first decision
+        loop.run(1)
+    else:
+        loop._round(True)
+        loop._counted = True
     t1 = ev()
     done, stop = loop.train(check_every=256)
     t2 = ev()
@@ -264,7 +323,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     dist.all_reduce(tokens_all)
     rounds = loop.rounds
     e.close()
-    del e, w, loop
+    del e, loop
 
     # end to end from pinned host memory through the same public pieces
     host = torch.empty(n_local, dtype=torch.uint8, pin_memory=True)
@@ -273,9 +332,8 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     del shard
     dist.barrier()
     t = time.perf_counter()
-    e, w = make(K)
+    e, loop2 = make(K)
     e.append_bytes(host, shard_off)
-    loop2 = ShardedBPE([w], TorchDistComm())
     done2, _ = loop2.train(check_every=256)
     m2, _, _ = e.merges(0, done2)
     torch.cuda.synchronize()
@@ -294,7 +352,8 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
             "config": {"workload": desc, "name": args.workload, "corpus_bytes": int(tokens_all.item()),
                        "rows": len(off) - 1, "merges_timed": done, "first_merge": 0, "stop_reason": int(stop),
                        "sharding": "contiguous document ranges by bytes; pair keys by hash owner",
-                       "rounds": rounds, "chunk_entries": 8192,
+                       "rounds": rounds, "chunk_entries": 4096,
+                       "round_driver": "native NCCL loop (stbpe_mg_run)" if native else "python rounds over torch.distributed",
                        "l2": "inputs larger than L2 (4 bytes x tokens per merge)", "tile_tokens": 1024},
             "pair_count": {"ms": count_ms, "gbs": 4.0 * float(tokens_all.item()) / (count_ms / 1e3) / 1e9,
                            "note": "local histogram + all-to-all + owner insert + first decision"},

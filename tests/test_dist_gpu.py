@@ -61,7 +61,7 @@ def test_emulated_ranks_on_one_gpu_match_oracle(world, cap):
         w.e.close()
 
 
-def _nccl_rank(rank, world, port, target, q):
+def _nccl_rank(rank, world, port, target, q, native=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
@@ -70,16 +70,26 @@ def _nccl_rank(rank, world, port, target, q):
         c = synth.config2_mixed(2 << 20, seed=3, lexicon=5000, mean_doc_bytes=2048)
         off = np.asarray(c.row_offsets)
         lo, hi = shard_rows(off, world)[rank]
-        w = _make_worker(c.data, off, lo, hi, rank, world, target, 4096, device=f"cuda:{rank}")
-        done, stop = ShardedBPE([w], TorchDistComm()).train(check_every=32)
-        m, cnt, _ = w.merges()
+        if native:
+            from supertoken_b200.dist import NativeLoop
+            n = int(off[hi] - off[lo])
+            e = Engine(max(n, 1), base_vocab=256, max_merges=target, device=f"cuda:{rank}",
+                       table_slots=1 << 18, world_size=world, rank=rank)
+            e.append_bytes(c.data[off[lo]:off[hi]], off[lo:hi + 1] - off[lo])
+            done, stop = NativeLoop(e, cap_per_peer=64).train(check_every=32)   # small chunks: extra rounds
+            m, cnt, _ = e.merges()
+        else:
+            w = _make_worker(c.data, off, lo, hi, rank, world, target, 4096, device=f"cuda:{rank}")
+            done, stop = ShardedBPE([w], TorchDistComm()).train(check_every=32)
+            m, cnt, _ = w.merges()
         q.put((rank, m, cnt.tolist(), done, stop))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpus_over_nccl_match_oracle():
+@pytest.mark.parametrize("native", [False, True])
+def test_two_gpus_over_nccl_match_oracle(native):
     import torch.multiprocessing as mp
     world, target = 2, 80
     c = synth.config2_mixed(2 << 20, seed=3, lexicon=5000, mean_doc_bytes=2048)
@@ -89,7 +99,7 @@ def test_two_gpus_over_nccl_match_oracle():
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, target, q)) for r in range(world)]
+    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, target, q, native)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
