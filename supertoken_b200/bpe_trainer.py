@@ -182,6 +182,38 @@ class GPUBPETrainer(BaseTrainer):
         self._seed_warm_start_merges = list(coerced)
         self.freeze_warm_start = bool(freeze)
 
+    @classmethod
+    def precompute_warm_start_plan(cls, batches: Iterable, top_k: int, device=None) -> dict:
+        """Warm-start plan from the bigram histogram of the batches: the ``top_k`` most frequent
+        pairs (``gpu_tokenizer/bpe_trainer.py:2165-2252`` over ``ngram_stats.compute_ngram_histograms``,
+        order 2 = the adjacent-pair histogram the engine builds anyway).  Equal counts are ordered by
+        the smaller packed key, which makes the plan deterministic."""
+        empty = {"merges": [], "counts": [], "top_k": 0, "requested_top_k": int(top_k or 0), "order": 2,
+                 "histogram_size": 0, "source": "ngram"}
+        if top_k is None or top_k <= 0:
+            return empty
+        flat = [_flatten_batch(b) for b in batches]
+        total = sum(int(ids.numel()) for ids, _ in flat)
+        eng = Engine(max(total, 1), base_vocab=0, max_merges=1,
+                     device=torch.device(device) if device is not None else None)
+        try:
+            for ids, off in flat:
+                if ids.numel():
+                    eng.append_ids(ids, off)
+            eng.count_initial()
+            keys, counts = eng.export_histogram()
+        finally:
+            eng.close()
+        if keys.numel() == 0:
+            return empty
+        limit = min(int(top_k), int(keys.numel()))
+        # keys come out ascending: a stable sort by descending count keeps ties in key order
+        order = torch.argsort(counts, descending=True, stable=True)[:limit]
+        ks, cs = keys[order].cpu().tolist(), counts[order].cpu().tolist()
+        merges = [((k >> 32) & 0xFFFFFFFF, k & 0xFFFFFFFF) for k in ks]
+        return {"merges": merges, "counts": [int(c) for c in cs], "top_k": len(merges),
+                "requested_top_k": int(top_k), "order": 2, "histogram_size": int(keys.numel()), "source": "ngram"}
+
     # ------------------------------------------------------------------ the loop
     def _make_engine(self, n_tokens: int) -> Engine:
         dev = torch.device(self.device)
@@ -202,6 +234,18 @@ class GPUBPETrainer(BaseTrainer):
         CUDA tensors, as the reference's batchers yield them (``gpu_tokenizer/datasets.py:88-92``)."""
         if checkpoint_interval is not None and checkpoint_dir is None:
             raise ValueError("checkpoint_interval requires checkpoint_dir")
+        if resume_state is not None:
+            # resume (bpe_trainer.py:2938-2986): the merges of the checkpoint are replayed on the
+            # batches without counting, then the loop continues; merges are a pure function of the
+            # corpus, so the result equals an uninterrupted run
+            self.load_state_dict(resume_state)
+            warm_start_merges = list(self.merges)
+        elif warm_start_merges is None and warm_start_plan is not None:
+            warm_start_merges = [tuple(p) for p in warm_start_plan.get("merges", [])]
+        elif warm_start_merges is None and warm_start_ngrams:
+            batches = list(batches)
+            plan = self.precompute_warm_start_plan(batches, int(warm_start_ngrams), device=warm_start_device or self.device)
+            warm_start_merges = plan["merges"]
         flat: List[Tuple[torch.Tensor, np.ndarray]] = [_flatten_batch(b) for b in batches]
         total = sum(int(ids.numel()) for ids, _ in flat)
         t0 = time.perf_counter()

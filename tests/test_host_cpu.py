@@ -75,3 +75,19 @@ def test_privacy_helpers():
     assert t.randomize_ties and t._privacy_summary()["mode"] == "tie-randomize"
     with pytest.raises(ValueError):
         GPUBPETrainer(device="cuda:0").fit([], checkpoint_interval=5)
+
+
+def test_cli_parses_the_reference_flags(tmp_path):
+    from supertoken_b200 import cli
+    (tmp_path / "a.txt").write_bytes(b"hello world")
+    args = cli.build_parser().parse_args(
+        ["train-bpe", "--data", str(tmp_path / "*.txt"), "--bos", "1", "--eos", "2", "--seed", "3", "--device", "cuda",
+         "--merges", "10", "--base-vocab", "256", "--target-util", "0.5", "--min-batch", "1", "--max-batch", "8",
+         "--token-bytes", "1024", "--log-every", "5", "--out-dir", str(tmp_path / "o"), "--privacy", "--privacy-salt", "s",
+         "--tie-seed", "4", "--checkpoint-dir", str(tmp_path / "c"), "--checkpoint-every", "5", "--dry-run",
+         "--warm-start", "3", "--io-workers", "2", "--prefetch-batches", "2", "--prefetch-jitter", "0.1", "--code-mode",
+         "--meta-compress", "--aug-strength", "0.2"])
+    assert args.merges == 10 and args.privacy and args.dry_run
+    assert cli.main(["train-bpe", "--data", str(tmp_path / "*.txt"), "--dry-run"]) == 0
+    data, off = cli.load_rows([str(tmp_path / "a.txt")], 300, None)
+    assert data.dtype == np.int32 and data[0] == 300 and off.tolist() == [0, 12]

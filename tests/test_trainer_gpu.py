@@ -105,3 +105,44 @@ def test_fit_bytes_and_artifacts(tmp_path):
     assert t2.merges == om
     t3 = GPUBPETrainer(merges=64, device="cuda:0", warm_start_merges=om[:20])
     assert t3.fit_bytes(c.data, c.row_offsets)["merges"] == om
+
+
+def test_resume_equals_uninterrupted_run_and_warm_start_plan(tmp_path):
+    c = synth.config2_mixed(1 << 18, seed=21, lexicon=1500, mean_doc_bytes=600)
+    rows = [r.tolist() for r in corpus_rows(c)]
+    batches = [make_batch(rows[:len(rows) // 2]), make_batch(rows[len(rows) // 2:])]
+    full = GPUBPETrainer(merges=50, device="cuda")
+    full.fit(batches, log_every=0)
+    half = GPUBPETrainer(merges=20, device="cuda")
+    half.fit(batches, log_every=0)
+    half.save_checkpoint(tmp_path / "ck")
+    resumed = GPUBPETrainer(merges=50, device="cuda")
+    state = json.load(open(tmp_path / "ck" / "state.json"))
+    state["trainer"]["target_merges"] = 50
+    resumed.fit(batches, log_every=0, resume_state=state)
+    assert resumed.merges == full.merges and resumed.vocab_size == full.vocab_size
+    # warm-start plan = the top-k bigrams of the initial histogram (ties to the smaller key)
+    ids, off = O.flatten_rows(rows)
+    k, cnt = O.count_pairs_flat(ids, off, 1)
+    order = sorted(range(len(k)), key=lambda i: (-int(cnt[i]), int(k[i])))[:7]
+    plan = GPUBPETrainer.precompute_warm_start_plan(batches, 7, device="cuda")
+    assert plan["merges"] == [(int(k[i]) >> 32, int(k[i]) & 0xFFFFFFFF) for i in order]
+    assert plan["counts"] == [int(cnt[i]) for i in order] and plan["histogram_size"] == len(k)
+    assert plan["merges"][0] == full.merges[0]
+
+
+def test_cli_train_bpe(tmp_path):
+    from supertoken_b200 import cli
+    c = synth.config1_text(1 << 16, seed=2, file_bytes=1 << 13)
+    off = np.asarray(c.row_offsets)
+    for i in range(len(off) - 1):
+        (tmp_path / f"part{i:02d}.txt").write_bytes(np.asarray(c.data)[off[i]:off[i + 1]].tobytes())
+    out = tmp_path / "tok"
+    rc = cli.main(["train-bpe", "--data", str(tmp_path / "part*.txt"), "--merges", "30", "--out-dir", str(out),
+                   "--log-every", "0", "--io-workers", "4", "--target-util", "0.8"])
+    assert rc == 0
+    om, _, _ = O.train_flat(*O.flatten_rows(corpus_rows(c)), 256, 30, 1)
+    meta = json.load(open(out / "bpe_merges.json"))
+    assert [tuple(m) for m in meta["merges"]] == om
+    assert open(out / "merges.txt", encoding="utf-8").read().splitlines()[0] == "#version: 0.2"
+    assert cli.main(["train-bpe", "--data", str(tmp_path / "nothing*"), "--out-dir", str(out)]) == 2
