@@ -38,7 +38,10 @@ struct stbpe_engine {
     bool own_boxes;
     float count_ms;       // device time of the histogram kernels of the last count
     cudaEvent_t ev0, ev1;
-    uint32_t *tiles_alt;  // second stream buffer, allocated at the first re-pack
+    uint32_t *tiles_alt;  // second stream buffer of the re-pack (at creation when memory allows)
+    i64 *rp_lens, *rp_offs;  // re-pack scratch: tile lengths and their exclusive sums
+    void *rp_tmp;
+    size_t rp_tmp_bytes;
     int repacks;
     cudaGraphExec_t graph;
     int graph_merges;
@@ -145,6 +148,9 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->graph = nullptr;
     e->graph_merges = 0;
     e->tiles_alt = nullptr;
+    e->rp_lens = e->rp_offs = nullptr;
+    e->rp_tmp = nullptr;
+    e->rp_tmp_bytes = 0;
     e->repacks = 0;
     e->count_ms = 0.f;
     e->ev0 = e->ev1 = nullptr;
@@ -204,6 +210,22 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     ALLOC(e->d.presence, (size_t)(STBPE_PROWS + 1) * e->d.presence_words);
     ALLOC(e->d.cand_bits, e->d.presence_words + 1);
     ALLOC(e->d.worklist, (size_t)e->max_tiles + 32);
+    // the re-pack allocates nothing inside the merge loop: its scratch is sized here for the largest
+    // stream, and the second stream buffer too unless it would take more than half of what is free
+    ALLOC(e->rp_lens, (size_t)e->max_tiles + 1);
+    ALLOC(e->rp_offs, (size_t)e->max_tiles + 1);
+    cub::DeviceScan::ExclusiveSum(nullptr, e->rp_tmp_bytes, e->rp_lens, e->rp_offs, e->max_tiles + 1, 0);
+    {
+        unsigned char *t = nullptr;
+        ALLOC(t, e->rp_tmp_bytes ? e->rp_tmp_bytes : 16);
+        e->rp_tmp = t;
+    }
+    {
+        size_t free_b = 0, total_b = 0;
+        const size_t want = (size_t)e->max_tiles * STBPE_TILE * sizeof(uint32_t);
+        if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && want <= free_b / 2)
+            ALLOC(e->tiles_alt, (size_t)e->max_tiles * STBPE_TILE);
+    }
     if (cfg->world_size > 1) {
         e->lslots = 1ull << 22;
         e->d.lmask = e->lslots - 1;
@@ -488,7 +510,6 @@ STBPE_VISIBLE int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *cou
 
 static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s) {
     if (e->d.n_tiles > 0) {
-        worklist_reset_kernel<<<1, 1, 0, s>>>(e->d);
         const int wl_words = (e->d.n_tiles + 31) / 32;
         int wl_grid = (wl_words + 1023) / 1024;
         if (wl_grid > 32) wl_grid = 32;
@@ -543,17 +564,15 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
     auto now = [&]() { cudaStreamSynchronize(s); return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); };
     double t_a = dbg ? now() : 0;
     if (!e->tiles_alt) CK(dev_alloc(e, &e->tiles_alt, (size_t)e->max_tiles * STBPE_TILE));
-    i64 *lens = nullptr, *offs = nullptr;
-    CK(cudaMallocAsync((void **)&lens, (size_t)(nt + 1) * sizeof(i64), s));
-    CK(cudaMallocAsync((void **)&offs, (size_t)(nt + 1) * sizeof(i64), s));
+    i64 *lens = e->rp_lens, *offs = e->rp_offs;
     CK(cudaMemsetAsync(lens + nt, 0, sizeof(i64), s));
     tile_lens_kernel<<<(nt + 255) / 256, 256, 0, s>>>(e->d, lens);
     CK(cudaGetLastError());
     size_t tmp_bytes = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, lens, offs, nt + 1, s);
-    void *tmp = nullptr;
-    CK(cudaMallocAsync(&tmp, tmp_bytes ? tmp_bytes : 16, s));
-    cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, lens, offs, nt + 1, s);
+    if (tmp_bytes > e->rp_tmp_bytes) return fail(e, STBPE_E_STATE, "re-pack scratch too small");
+    tmp_bytes = e->rp_tmp_bytes;
+    cub::DeviceScan::ExclusiveSum(e->rp_tmp, tmp_bytes, lens, offs, nt + 1, s);
     CK(cudaGetLastError());
     double t_b = dbg ? now() : 0;
     repack_copy_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, offs, e->tiles_alt);
@@ -562,9 +581,6 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
     i64 total = 0;
     CK(cudaMemcpyAsync(&total, offs + nt, sizeof(i64), cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
-    CK(cudaFreeAsync(lens, s));
-    CK(cudaFreeAsync(offs, s));
-    CK(cudaFreeAsync(tmp, s));
     uint32_t *old = e->d.tiles;
     e->d.tiles = e->tiles_alt;
     e->tiles_alt = old;
@@ -867,16 +883,16 @@ STBPE_VISIBLE int stbpe_mg_set_buffers(stbpe_engine *e, void *outbox, void *inbo
     e->d.outbox = (Slot *)outbox;
     e->d.inbox = (Slot *)inbox;
     e->d.cap_per_peer = cap_per_peer;
+    CK(cudaSetDevice(e->cfg.device));
+    outbox_reset_kernel<<<1, 64>>>(e->d);
+    CK(cudaGetLastError());
+    CK(cudaDeviceSynchronize());
     return STBPE_OK;
 }
 
 static int launch_drain(stbpe_engine *e, cudaStream_t s) {
     if (!e->d.outbox || e->d.cap_per_peer < 1) return fail(e, STBPE_E_STATE, "call stbpe_mg_set_buffers first");
-    outbox_reset_kernel<<<1, 64, 0, s>>>(e->d);
-    CK(cudaGetLastError());
-    drain_ltable_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d);
-    CK(cudaGetLastError());
-    ltouched_swap_kernel<<<e->sm_count, 256, 0, s>>>(e->d);
+    drain_ltable_kernel<<<e->sm_count * 2, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
     return STBPE_OK;
 }
@@ -932,14 +948,11 @@ STBPE_VISIBLE int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev, void *stre
     return STBPE_OK;
 }
 
-__global__ void set_target_if_unset_kernel(EngineDev e, int target) { e.st->target = target; }
-
 STBPE_VISIBLE int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev, void *stream) {
     if (!e || !all_cands_dev) return STBPE_E_BADARG;
     cudaStream_t s = (cudaStream_t)stream;
     CK(cudaSetDevice(e->cfg.device));
-    set_target_if_unset_kernel<<<1, 1, 0, s>>>(e->d, e->cfg.max_merges);
-    commit_kernel<<<1, 1, 0, s>>>(e->d, (const i64 *)all_cands_dev);
+    commit_kernel<<<1, 1, 0, s>>>(e->d, (const i64 *)all_cands_dev, e->cfg.max_merges);
     CK(cudaGetLastError());
     return STBPE_OK;
 }
@@ -1026,6 +1039,9 @@ STBPE_VISIBLE int stbpe_mg_nccl_init(stbpe_engine *e, const void *id128, int64_t
         CK(cudaMemset(e->d.inbox, 0, n * sizeof(Slot)));
         e->d.cap_per_peer = cap_per_peer;
         e->own_boxes = true;
+        outbox_reset_kernel<<<1, 64>>>(e->d);
+        CK(cudaGetLastError());
+        CK(cudaDeviceSynchronize());
     }
     // one communicator per process and device, shared by every engine created later with the same
     // world size and rank (setting one up costs far more than a training run of a small corpus)

@@ -232,6 +232,7 @@ __device__ __forceinline__ void begin_merge(const EngineDev &e, u64 key, i64 cou
     st->cur_new = new_id;
     st->cur_count = count;
     st->merges_done = mnum + 1;
+    st->n_work = 0;  // the worklist of this merge starts empty (worklist_kernel appends)
     const i64 h = find_slot(e, key);
     if (h >= 0) {
         e.table[h].count = 0;
@@ -383,14 +384,9 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
 // A partner in a tile that is not visited is dropped by the warp that owns the head (fix-up in the
 // merge kernel).  This kernel builds the bitmap of visited tiles and the compact worklist.
 // ---------------------------------------------------------------------------------------
-__global__ void worklist_reset_kernel(EngineDev e) {
-    if (e.st->stopped || e.st->exchange_only) return;
-    e.st->n_work = e.st->filter_stale ? -1 : 0;
-}
-
 __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
     DevState *st = e.st;
-    if (st->stopped || st->exchange_only || st->filter_stale) return;
+    if (st->stopped || st->exchange_only) return;
     unsigned int r1, r2;
     filter_rows(((u64)(uint32_t)st->cur_a << 32) | (u64)(uint32_t)st->cur_b, r1, r2);
     const unsigned int *row1 = e.presence + (size_t)r1 * e.presence_words;
@@ -557,6 +553,8 @@ __global__ void tile_lens_kernel(EngineDev e, i64 *lens) {
 // ---------------------------------------------------------------------------------------
 // multi-GPU: drain the rank-local delta table into per-owner outbox chunks; apply an inbox
 // ---------------------------------------------------------------------------------------
+// chunk headers start a round at zero: done once when the buffers are set and after every exchange
+// (apply_inbox_kernel), so a round needs no separate reset launch
 __global__ void outbox_reset_kernel(EngineDev e) {
     int p = blockIdx.x * blockDim.x + threadIdx.x;
     if (p < e.world) {
@@ -576,6 +574,7 @@ __global__ void outbox_reset_kernel(EngineDev e) {
 // (the header count of a chunk keeps counting past the capacity, which tells the receiver that
 // more is to come).
 __global__ void drain_ltable_kernel(EngineDev e) {
+    __shared__ int s_last;
     const unsigned int n = e.st->n_ltouched;
     unsigned int *kept = e.ltouched + (e.lmask + 1);
     for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -596,18 +595,32 @@ __global__ void drain_ltable_kernel(EngineDev e) {
         s->key = STBPE_EMPTY;
         s->count = 0;
     }
-}
-
-// the kept entries become the list the next inserts append to
-__global__ void ltouched_swap_kernel(EngineDev e) {
-    const unsigned int n = e.st->n_lkept;
-    const unsigned int *kept = e.ltouched + (e.lmask + 1);
-    for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
-        e.ltouched[i] = kept[i];
-    if (blockIdx.x == 0 && threadIdx.x == 0) e.st->n_ltouched = n;
+    // the last CTA to finish turns the kept entries into the list the next inserts append to
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = (atomicAdd(&e.st->ticket, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const unsigned int nk = *(volatile unsigned int *)&e.st->n_lkept;
+    for (unsigned int i = threadIdx.x; i < nk; i += blockDim.x) e.ltouched[i] = ((volatile unsigned int *)kept)[i];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        e.st->n_ltouched = nk;
+        e.st->n_lkept = 0;
+        e.st->ticket = 0;
+    }
 }
 
 __global__ void apply_inbox_kernel(EngineDev e) {
+    if (blockIdx.x == 0 && threadIdx.x < e.world) {  // the exchange is over: headers for the next round
+        Slot h;
+        h.key = 0;
+        h.count = 0;
+        e.outbox[(i64)threadIdx.x * (e.cap_per_peer + 1)] = h;
+    }
     for (int p = 0; p < e.world; ++p) {
         const Slot *chunk = e.inbox + (i64)p * (e.cap_per_peer + 1);
         i64 n = (i64)chunk[0].key;
@@ -625,8 +638,10 @@ __global__ void apply_inbox_kernel(EngineDev e) {
 // Every rank evaluates the same gathered candidates {key, count, incomplete, -} and reaches the
 // same decision: if any rank still has deltas in flight the next round only exchanges, otherwise
 // the best candidate (highest count, smallest key) is committed or a stop rule fires.
-__global__ void commit_kernel(EngineDev e, const i64 *all_cands) {
+__global__ void commit_kernel(EngineDev e, const i64 *all_cands, int target) {
     DevState *st = e.st;
+    st->target = target;
+    st->round_incomplete = 0;  // the candidates carried this round's flag; the next round starts clean
     if (st->stopped) return;
     u64 bk = STBPE_EMPTY;
     i64 bc = 0;
