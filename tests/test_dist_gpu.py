@@ -61,6 +61,25 @@ def test_emulated_ranks_on_one_gpu_match_oracle(world, cap):
         w.e.close()
 
 
+def test_emulated_ranks_repack_between_commit_and_apply():
+    """A rank re-packs its sparse tiles when the host looks at the progress, i.e. after a merge has
+    been committed and before the next round applies it: the worklist of that merge must be built
+    on the re-packed layout."""
+    world, target = 2, 80
+    c = synth.config2_mixed(2 << 20, seed=3, lexicon=5000, mean_doc_bytes=2048)
+    off = np.asarray(c.row_offsets)
+    om, oc, _ = O.train_flat(*O.flatten_rows(corpus_rows(c)), 256, target, 1)
+    workers = [_make_worker(c.data, off, lo, hi, r, world, target, 4096)
+               for r, (lo, hi) in enumerate(shard_rows(off, world))]
+    done, stop = ShardedBPE(workers, LocalComm()).train(check_every=8)
+    assert done == target and stop == L.STOP_TARGET
+    assert sum(w.e.state().repacks for w in workers) > 0
+    for w in workers:
+        m, cnt, _ = w.merges()
+        assert m == om and cnt.tolist() == oc
+        w.e.close()
+
+
 def _nccl_rank(rank, world, port, target, q, native=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
