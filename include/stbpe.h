@@ -180,6 +180,30 @@ int stbpe_mg_nccl_unique_id(void *out128);
 int stbpe_mg_nccl_init(stbpe_engine *e, const void *id128, int64_t cap_per_peer);
 int stbpe_mg_run(stbpe_engine *e, int first, int n_rounds, void *stream);
 
+/* The same rounds with the exchange done by the kernels themselves over NVLink peer memory, one
+ * process per GPU, no library collective inside a round.  Replaces the histogram reduce of the
+ * reference (gpu_tokenizer/utils.py:863-978, one NCCL all-reduce per count) on this path.
+ *   stbpe_mg_peer_export : allocates this rank's mailbox (header + one chunk of cap_per_peer entries
+ *                          per sender) and returns its 64-byte CUDA IPC handle; the caller gathers the
+ *                          handles of all ranks (any host transport)
+ *   stbpe_mg_peer_open   : maps the mailboxes of the other ranks (handles: world x 64 bytes, indexed by
+ *                          rank; the own entry is ignored)
+ *   stbpe_mg_peer_run    : enqueue n_rounds rounds (first != 0: round 0 is the local count); batches of
+ *                          16 rounds replay as one CUDA graph.  Every rank must enqueue the same number
+ *                          of rounds, and the ranks should start them within a second of one another:
+ *                          a kernel waits at most two seconds for a peer's flag, then records a time-out
+ *                          that the next stbpe_get_state / error check reports (STBPE_E_TIMEOUT); the
+ *                          engine is then unusable.  Does not synchronise.
+ *   stbpe_mg_peer_close  : unmaps the peers' mailboxes; call on every rank and synchronise the ranks
+ *                          before any of them destroys its engine.
+ * At most 16 ranks.  Never run two ranks of one job on the same GPU with these entry points (the
+ * kernels of different ranks wait for one another); stbpe_mg_set_buffers + the step-wise entry
+ * points above serve that case. */
+int stbpe_mg_peer_export(stbpe_engine *e, int64_t cap_per_peer, void *handle_out64);
+int stbpe_mg_peer_open(stbpe_engine *e, const void *handles, int32_t n_handles);
+int stbpe_mg_peer_run(stbpe_engine *e, int first, int n_rounds, void *stream);
+int stbpe_mg_peer_close(stbpe_engine *e);
+
 /* Stateless operators on padded [B, L] batches resident on the device, with the
  * reference's operator signatures.
  * stbpe_rows_count_pairs  <- utils.count_pairs (gpu_tokenizer/utils.py:691-706): unique

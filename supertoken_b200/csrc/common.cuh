@@ -82,7 +82,22 @@ struct DevState {
     int round_incomplete;      // multi-GPU: this rank saw a full chunk or kept entries this round
 };
 
+// Peer mailboxes (multi-GPU exchange over NVLink peer memory, no library collective).  Every rank owns
+// one mailbox in its own HBM that its peers map: a header of flags and candidates followed by one
+// inbox chunk per sender.  Flags carry the round number and only grow, so nothing is ever reset.
+#define STBPE_MAX_PEERS 16
+#define STBPE_MAIL_HEADER_BYTES 2048
+struct MailHeader {
+    u64 inbox_flag[STBPE_MAX_PEERS];     // [src] = last round whose chunk from src is complete here
+    u64 cand_flag[STBPE_MAX_PEERS];      // [src] = last round whose candidate from src is here
+    i64 cands[STBPE_MAX_PEERS][4];       // [src] = {key, count, incomplete, -}
+    u64 round;                           // rounds this rank has committed (own use only)
+    unsigned int out_count[STBPE_MAX_PEERS];  // entries sent to each owner this round (own use only)
+};
+static_assert(sizeof(MailHeader) <= STBPE_MAIL_HEADER_BYTES, "mailbox header does not fit");
+
 struct EngineDev {
+    unsigned char *mail[STBPE_MAX_PEERS];  // mailbox of every rank ([rank] = own), or null
     uint32_t *tiles;
     TileRec *recs;  // 2 per tile
     int n_tiles;
@@ -119,6 +134,14 @@ struct EngineDev {
     Slot *inbox;
     i64 cap_per_peer;
 };
+
+__device__ __forceinline__ MailHeader *mail_header(const EngineDev &e, int r) {
+    return reinterpret_cast<MailHeader *>(e.mail[r]);
+}
+// chunk that rank `src` fills in the mailbox of rank `dst`
+__device__ __forceinline__ Slot *mail_chunk(const EngineDev &e, int dst, int src) {
+    return reinterpret_cast<Slot *>(e.mail[dst] + STBPE_MAIL_HEADER_BYTES) + (i64)src * (e.cap_per_peer + 1);
+}
 
 __device__ __forceinline__ u64 mix64(u64 x) {
     x ^= x >> 33;

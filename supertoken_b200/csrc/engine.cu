@@ -36,6 +36,9 @@ struct stbpe_engine {
     ncclComm_t comm;      // own NCCL communicator for the native multi-GPU round loop
     i64 *all_cands;       // world x 4 gathered candidates (native loop)
     bool own_boxes;
+    unsigned char *mail_own;               // this rank's mailbox (peer-memory rounds)
+    void *mail_mapped[STBPE_MAX_PEERS];    // peers' mailboxes as mapped into this process
+    bool peers_open;
     float count_ms;       // device time of the histogram kernels of the last count
     cudaEvent_t ev0, ev1;
     uint32_t *tiles_alt;  // second stream buffer of the re-pack (at creation when memory allows)
@@ -114,6 +117,11 @@ STBPE_VISIBLE int stbpe_destroy(stbpe_engine *e) {
     if (!e) return STBPE_OK;
     cudaSetDevice(e->cfg.device);
     if (e->graph) cudaGraphExecDestroy(e->graph);
+    for (void *&m : e->mail_mapped)
+        if (m) {
+            cudaIpcCloseMemHandle(m);
+            m = nullptr;
+        }
     // the NCCL communicator is shared by the engines of this process and lives until exit
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
@@ -157,6 +165,9 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->comm = nullptr;
     e->all_cands = nullptr;
     e->own_boxes = false;
+    e->mail_own = nullptr;
+    memset(e->mail_mapped, 0, sizeof(e->mail_mapped));
+    e->peers_open = false;
     e->use_graph = getenv("STBPE_NO_GRAPH") == nullptr;
     memset(&e->d, 0, sizeof(e->d));
     auto bail = [&](int code) {
@@ -954,6 +965,149 @@ STBPE_VISIBLE int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev, vo
     CK(cudaSetDevice(e->cfg.device));
     commit_kernel<<<1, 1, 0, s>>>(e->d, (const i64 *)all_cands_dev, e->cfg.max_merges);
     CK(cudaGetLastError());
+    return STBPE_OK;
+}
+
+
+// ------------------------------------------------------------------ rounds over peer memory
+// The exchange of a round done by the kernels themselves: every rank owns a mailbox that its peers
+// map through CUDA IPC; drain_peer_kernel stores the deltas into the owners' mailboxes,
+// select_kernel (mode 3) stores the candidate into every mailbox, and apply_peer_kernel /
+// commit_peer_kernel wait (bounded, two seconds) for the senders' flags.  A round is six launches
+// and nothing else, so batches of rounds replay as one CUDA graph.  One rank per GPU only.
+STBPE_VISIBLE int stbpe_mg_peer_export(stbpe_engine *e, int64_t cap_per_peer, void *handle_out64) {
+    if (!e || !handle_out64 || cap_per_peer < 1) return STBPE_E_BADARG;
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    if (e->cfg.world_size > STBPE_MAX_PEERS) return fail(e, STBPE_E_BADARG, "at most 16 ranks share mailboxes");
+    if (e->d.cap_per_peer != 0 && e->d.cap_per_peer != cap_per_peer)
+        return fail(e, STBPE_E_STATE, "exchange buffers of another capacity are already set");
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->mail_own) {
+        const size_t bytes = STBPE_MAIL_HEADER_BYTES + (size_t)e->cfg.world_size * (cap_per_peer + 1) * sizeof(Slot);
+        cudaError_t c = dev_alloc(e, &e->mail_own, bytes);
+        if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc mailbox");
+        CK(cudaMemset(e->mail_own, 0, bytes));
+        CK(cudaDeviceSynchronize());
+        e->d.cap_per_peer = cap_per_peer;
+    }
+    cudaIpcMemHandle_t h;
+    CK(cudaIpcGetMemHandle(&h, e->mail_own));
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    memcpy(handle_out64, &h, sizeof(h));
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_peer_open(stbpe_engine *e, const void *handles, int32_t n_handles) {
+    if (!e || !handles) return STBPE_E_BADARG;
+    if (!e->mail_own) return fail(e, STBPE_E_STATE, "call stbpe_mg_peer_export first");
+    if (n_handles != e->cfg.world_size) return fail(e, STBPE_E_BADARG, "one handle per rank is needed");
+    if (e->peers_open) return STBPE_OK;
+    CK(cudaSetDevice(e->cfg.device));
+    for (int r = 0; r < n_handles; ++r) {
+        if (r == e->cfg.rank) {
+            e->d.mail[r] = e->mail_own;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)r * sizeof(h), sizeof(h));
+        void *p = nullptr;
+        CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        e->mail_mapped[r] = p;
+        e->d.mail[r] = (unsigned char *)p;
+    }
+    e->peers_open = true;
+    return STBPE_OK;
+}
+
+// Unmap the peers' mailboxes (call on every rank, then synchronise the ranks, before any of them
+// destroys its engine).
+STBPE_VISIBLE int stbpe_mg_peer_close(stbpe_engine *e) {
+    if (!e) return STBPE_E_BADARG;
+    CK(cudaSetDevice(e->cfg.device));
+    CK(cudaDeviceSynchronize());
+    if (e->graph) {
+        cudaGraphExecDestroy(e->graph);
+        e->graph = nullptr;
+    }
+    for (int r = 0; r < STBPE_MAX_PEERS; ++r) {
+        if (e->mail_mapped[r]) {
+            CK(cudaIpcCloseMemHandle(e->mail_mapped[r]));
+            e->mail_mapped[r] = nullptr;
+        }
+        if (r != e->cfg.rank) e->d.mail[r] = nullptr;
+    }
+    e->peers_open = false;
+    return STBPE_OK;
+}
+
+static int enqueue_peer_round(stbpe_engine *e, bool count_round, cudaStream_t s) {
+    int rc = count_round ? launch_count(e, true, s) : launch_merge(e, true, s);
+    if (rc != STBPE_OK) return rc;
+    drain_peer_kernel<<<e->sm_count * 2, 256, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    apply_peer_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d);
+    CK(cudaGetLastError());
+    rc = launch_refresh(e, 0, s);
+    if (rc != STBPE_OK) return rc;
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 3, 0, e->cand);
+    CK(cudaGetLastError());
+    commit_peer_kernel<<<1, 32, 0, s>>>(e->d, e->cfg.max_merges);
+    CK(cudaGetLastError());
+    return STBPE_OK;
+}
+
+// first != 0: round 0 counts the local rows.  Enqueues n_rounds rounds; no host synchronisation.
+// Every rank must enqueue the same number of rounds.
+STBPE_VISIBLE int stbpe_mg_peer_run(stbpe_engine *e, int first, int n_rounds, void *stream) {
+    if (!e || n_rounds < 0) return STBPE_E_BADARG;
+    if (!e->peers_open) return fail(e, STBPE_E_STATE, "call stbpe_mg_peer_open first");
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    int r = 0;
+    if (first && n_rounds > 0) {
+        int rc = enqueue_peer_round(e, true, s);
+        if (rc != STBPE_OK) return rc;
+        e->counted = true;
+        ++r;
+    }
+    const int G = 16;  // rounds per graph replay
+    while (r < n_rounds) {
+        if (e->use_graph && n_rounds - r >= G) {
+            if (e->graph && (e->graph_merges != e->d.n_tiles || e->graph_tiles != e->d.tiles)) {
+                cudaGraphExecDestroy(e->graph);
+                e->graph = nullptr;
+            }
+            if (!e->graph) {
+                cudaStream_t cs;
+                CK(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
+                cudaGraph_t g;
+                CK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+                int rc2 = STBPE_OK;
+                for (int i = 0; i < G && rc2 == STBPE_OK; ++i) rc2 = enqueue_peer_round(e, false, cs);
+                cudaError_t ce = cudaStreamEndCapture(cs, &g);
+                if (rc2 != STBPE_OK) {
+                    cudaStreamDestroy(cs);
+                    return rc2;
+                }
+                if (ce != cudaSuccess) {
+                    cudaStreamDestroy(cs);
+                    return cuda_fail(e, ce, "cudaStreamEndCapture");
+                }
+                ce = cudaGraphInstantiate(&e->graph, g, 0);
+                cudaGraphDestroy(g);
+                cudaStreamDestroy(cs);
+                if (ce != cudaSuccess) return cuda_fail(e, ce, "cudaGraphInstantiate");
+                e->graph_merges = e->d.n_tiles;
+                e->graph_tiles = e->d.tiles;
+            }
+            CK(cudaGraphLaunch(e->graph, s));
+            r += G;
+        } else {
+            int rc = enqueue_peer_round(e, false, s);
+            if (rc != STBPE_OK) return rc;
+            ++r;
+        }
+    }
     return STBPE_OK;
 }
 

@@ -293,6 +293,10 @@ __device__ __forceinline__ void block_best(u64 &bk, i64 &bc, u64 *s_k, i64 *s_c)
     __syncthreads();
 }
 
+#include "peer_kernels.cuh"
+
+// mode 0: peek (result into the state); 1: single rank, advance or stop; 2: candidate of this rank
+// into cand; 3: candidate of this rank into every peer mailbox
 __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
     select_kernel(EngineDev e, int mode, int all2, i64 *cand) {
     DevState *st = e.st;
@@ -367,11 +371,13 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
         st->peek_count = bc;
     } else if (mode == 1) {
         advance_or_stop(e, bk, bc);
-    } else {
+    } else if (mode == 2) {
         cand[0] = (i64)bk;
         cand[1] = bc;
         cand[2] = st->round_incomplete;
         cand[3] = 0;
+    } else {
+        publish_candidate(e, bk, bc, st->round_incomplete);
     }
 }
 

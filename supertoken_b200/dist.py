@@ -248,6 +248,69 @@ class NativeLoop:
             self.run(check_every)
 
 
+class PeerLoop:
+    """Rounds whose exchange the kernels do themselves over NVLink peer memory
+    (``stbpe_mg_peer_run``): every rank's mailbox is mapped by its peers through CUDA IPC, a round
+    is six kernel launches and no collective, and batches of rounds replay as one CUDA graph.
+    ``torch.distributed`` is used on the host only: once to hand round the IPC handles, and for a
+    barrier before each batch so that the ranks start it together (a kernel waits at most two
+    seconds for a peer).  One engine (one GPU) per process; never two ranks on one GPU."""
+
+    def __init__(self, engine, cap_per_peer: int = 4096, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.e = engine
+        self._lib = L.load()
+        world = engine.world_size
+        if dist.get_world_size(group) != world or dist.get_rank(group) != engine.rank:
+            raise ValueError("the engine's world size / rank differ from the process group's")
+        buf = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(engine.device):
+            engine._check(self._lib.stbpe_mg_peer_export(engine._h, int(cap_per_peer), buf))
+        mine = torch.tensor(list(buf), dtype=torch.uint8, device=engine.device)
+        every = torch.empty(world * 64, dtype=torch.uint8, device=engine.device)
+        dist.all_gather_into_tensor(every, mine, group=group)
+        raw = bytes(every.cpu().tolist())
+        with torch.cuda.device(engine.device):
+            engine._check(self._lib.stbpe_mg_peer_open(engine._h, raw, world))
+        self._open = True
+        self.rounds = 0
+        self._counted = False
+
+    def run(self, n_rounds: int):
+        first = 0 if self._counted else 1
+        self.dist.barrier(group=self.group)
+        with torch.cuda.device(self.e.device):
+            self.e._check(self._lib.stbpe_mg_peer_run(self.e._h, first, int(n_rounds), self.e._s))
+        self._counted = True
+        self.rounds += n_rounds
+
+    def progress(self) -> Tuple[int, int]:
+        self.e.repack()
+        st = self.e.state()
+        if st.device_error:
+            self.e.count_error()
+        return int(st.merges_done), int(st.stop_reason)
+
+    def train(self, check_every: int = 256):
+        if not self._counted:
+            self.run(1)
+        while True:
+            done, reason = self.progress()
+            if reason != L.RUNNING:
+                return done, reason
+            self.run(check_every)
+
+    def close(self):
+        """Unmap the peers' mailboxes and wait for every rank to have done so; only then may a
+        rank destroy its engine (its mailbox must outlive the peers' mappings)."""
+        if self._open:
+            with torch.cuda.device(self.e.device):
+                self.e._check(self._lib.stbpe_mg_peer_close(self.e._h))
+            self.dist.barrier(group=self.group)
+            self._open = False
+
+
 # ----------------------------------------------------------------------------- bench (N > 1)
 def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     """``bench.py`` at N > 1: the same corpus as N = 1, rows sharded over the ranks (strong
@@ -273,14 +336,26 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     torch.cuda.empty_cache()
     n_local = int(shard.numel())
 
-    native = not os.environ.get("STBPE_MG_PYTHON_ROUNDS")
+    # round driver: kernels over peer memory (default), the native NCCL loop, or Python rounds
+    driver = os.environ.get("STBPE_MG_DRIVER", "peer")
+    if os.environ.get("STBPE_MG_PYTHON_ROUNDS"):
+        driver = "python"
+    native = driver != "python"
+    launches_per_round = {"peer": 7, "nccl": 7, "python": 7}[driver]
 
     def make(max_merges):
         e = Engine(max(n_local, 1), base_vocab=256, max_merges=max(max_merges, 1), device=dev,
                    world_size=world, rank=rank)
-        if native:
+        if driver == "peer":
+            return e, PeerLoop(e, cap_per_peer=4096)
+        if driver == "nccl":
             return e, NativeLoop(e, cap_per_peer=4096)
         return e, ShardedBPE([EngineWorker(e, cap_per_peer=4096)], TorchDistComm())
+
+    def finish(e, loop):
+        if hasattr(loop, "close"):
+            loop.close()
+        e.close()
 
     def ev():
         x = torch.cuda.Event(enable_timing=True)
@@ -296,13 +371,18 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     e, loop = make(W)
     e.append_bytes(shard, shard_off)
     loop.train(check_every=8)
-    e.close()
+    finish(e, loop)
     del e, loop
 
     e, loop = make(K)
     e.append_bytes(shard, shard_off)
     torch.cuda.synchronize()
     dist.barrier()
+    sampler = None
+    if rank == 0:
+        from bench import ClockSampler  # type: ignore
+        sampler = ClockSampler(local_rank)
+        sampler.start()
     t0 = ev()
     if native:                      # initial histogram + exchange + first decision
         loop.run(1)
@@ -313,6 +393,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     done, stop = loop.train(check_every=256)
     t2 = ev()
     torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
     dist.barrier()
     count_ms = synced_max(t0.elapsed_time(t1))
     loop_ms = synced_max(t1.elapsed_time(t2))
@@ -322,7 +403,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     tokens_all = torch.tensor([float(n_local)], dtype=torch.float64, device=dev)
     dist.all_reduce(tokens_all)
     rounds = loop.rounds
-    e.close()
+    finish(e, loop)
     del e, loop
 
     # end to end from pinned host memory through the same public pieces
@@ -339,6 +420,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     torch.cuda.synchronize()
     e2e_s = synced_max((time.perf_counter() - t) * 1000.0) / 1000.0
     assert m2 == merges_gpu, "merge list changed between two runs on the same input"
+    finish(e, loop2)
 
     if rank == 0:
         from bench import peaks  # type: ignore
@@ -353,18 +435,20 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
                        "rows": len(off) - 1, "merges_timed": done, "first_merge": 0, "stop_reason": int(stop),
                        "sharding": "contiguous document ranges by bytes; pair keys by hash owner",
                        "rounds": rounds, "chunk_entries": 4096,
-                       "round_driver": "native NCCL loop (stbpe_mg_run)" if native else "python rounds over torch.distributed",
+                       "round_driver": {"peer": "kernels over NVLink peer memory, CUDA graph of 16 rounds (stbpe_mg_peer_run)",
+                                        "nccl": "native NCCL loop (stbpe_mg_run)",
+                                        "python": "python rounds over torch.distributed"}[driver],
                        "l2": "inputs larger than L2 (4 bytes x tokens per merge)", "tile_tokens": 1024},
             "pair_count": {"ms": count_ms, "gbs": 4.0 * float(tokens_all.item()) / (count_ms / 1e3) / 1e9,
                            "note": "local histogram + all-to-all + owner insert + first decision"},
-            "roofline": {"bound": "hbm", "kernel": "merge round (all kernels and both collectives)",
+            "roofline": {"bound": "hbm", "kernel": "merge round (all kernels and the exchange)",
                          "achieved": algo / (loop_ms / 1e3) / 1e9, "peak": peak * world, "peak_kind": peak_kind,
                          "unit": "GB/s", "frac": algo / (loop_ms / 1e3) / 1e9 / (peak * world),
                          "algorithmic_bytes": algo, "traffic": None},
             "e2e": {"value": done2 / e2e_s, "unit": "merges/s", "seconds": e2e_s,
                     "h2d_bytes_per_step": float(tokens_all.item()) / max(done2, 1), "d2h_bytes_per_step": 24.0},
-            "gpu_launches": rounds * 9,
-            "clocks": None, "cpu_baseline": None,
+            "gpu_launches": rounds * launches_per_round,
+            "clocks": clocks, "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

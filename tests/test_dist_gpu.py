@@ -1,7 +1,9 @@
 """Multi-rank engine kernels (rank-local delta table, per-owner outbox, inbox apply, candidate,
 commit) against the single-process oracle.  With one GPU the ranks are emulated as several engines
 of one process whose kernels run one after the other (LocalComm copies the chunks); with two or
-more GPUs the same loop runs as one process per GPU over NCCL."""
+more GPUs the same loop runs as one process per GPU: over NCCL (Python rounds and the native loop)
+and with the exchange done by the kernels over NVLink peer memory.  The peer-memory kernels wait for
+one another and therefore never run with two ranks on one GPU."""
 import os
 import socket
 
@@ -81,33 +83,43 @@ def test_emulated_ranks_repack_between_commit_and_apply():
 
 
 def _nccl_rank(rank, world, port, target, q, native=False):
+    import datetime
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     try:
         c = synth.config2_mixed(2 << 20, seed=3, lexicon=5000, mean_doc_bytes=2048)
         off = np.asarray(c.row_offsets)
         lo, hi = shard_rows(off, world)[rank]
         if native:
-            from supertoken_b200.dist import NativeLoop
+            from supertoken_b200.dist import NativeLoop, PeerLoop
             n = int(off[hi] - off[lo])
             e = Engine(max(n, 1), base_vocab=256, max_merges=target, device=f"cuda:{rank}",
                        table_slots=1 << 18, world_size=world, rank=rank)
             e.append_bytes(c.data[off[lo]:off[hi]], off[lo:hi + 1] - off[lo])
-            done, stop = NativeLoop(e, cap_per_peer=64).train(check_every=32)   # small chunks: extra rounds
+            cls = PeerLoop if native == "peer" else NativeLoop
+            loop = cls(e, cap_per_peer=64)                    # small chunks: extra rounds
+            done, stop = loop.train(check_every=32)
             m, cnt, _ = e.merges()
+            if native == "peer":
+                assert loop.rounds > target + 1
+                loop.close()
         else:
             w = _make_worker(c.data, off, lo, hi, rank, world, target, 4096, device=f"cuda:{rank}")
             done, stop = ShardedBPE([w], TorchDistComm()).train(check_every=32)
             m, cnt, _ = w.merges()
         q.put((rank, m, cnt.tolist(), done, stop))
+    except Exception as exc:   # the parent ends the other rank instead of waiting for it
+        q.put((rank, "error", repr(exc), 0, 0))
+        raise
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("native", [False, True])
+@pytest.mark.parametrize("native", [False, True, "peer"])
 def test_two_gpus_over_nccl_match_oracle(native):
     import torch.multiprocessing as mp
     world, target = 2, 80
@@ -121,8 +133,16 @@ def test_two_gpus_over_nccl_match_oracle(native):
     procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, target, q, native)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in range(world)]
+    results = []
+    for _ in range(world):
+        results.append(q.get(timeout=240))
+        if results[-1][1] == "error":
+            break
+    failed = [r for r in results if r[1] == "error"]
     for p in procs:
-        p.join(timeout=60)
+        p.join(timeout=5 if failed else 60)
+        if p.is_alive():
+            p.terminate()
+    assert not failed, failed
     for rank, m, cnt, done, stop in results:
         assert m == om and cnt == oc and done == target and stop == L.STOP_TARGET
