@@ -42,6 +42,8 @@ WORKLOADS = {
     "c1": ("config1_text", 16 << 20, 0, 1000, "16 MiB lowercase Zipf(1.07) text, 16 rows of 1 MiB, 1000 merges"),
     "c5": ("config5_adversarial", 512 << 20, 4, 8000, "512 MiB runs/text/random bytes, 8000 merges"),
     "c4": ("config2_mixed", 8 << 30, 3, 50000, "8 GiB mixed text (as c2), 50000 merges"),
+    # count-only microbenchmark: a step is one full histogram pass (N = 1 only); "bytes" = tokens here
+    "c3": ("config3_ids", 1 << 31, 2, 5, "2^31 int32 ids Zipf(1.1) over 65 536, rows ~2048 tokens, one histogram pass per step"),
 }
 
 
@@ -153,6 +155,29 @@ def run_reference_arm(args, wl):
         return
     from supertoken_b200 import synth
     gen, n_bytes, seed, merges, desc = wl
+    if args.workload == "c3":
+        from oracle import oracle as O
+        n = min(1 << 25, n_bytes)
+        ids, off = synth.config3_ids(n, seed=seed)
+        ids, off = np.asarray(ids), np.asarray(off)
+        ts = []
+        for it in range(args.warmup + args.steps):
+            t = time.perf_counter()
+            O.count_pairs_flat(ids, off, 1)
+            if it >= args.warmup:
+                ts.append(time.perf_counter() - t)
+        med = float(np.median(ts))
+        gbs = 4.0 * n / med / 1e9
+        print(json.dumps({
+            "impl": "reference", "metric": "pair_count_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": med * 1e3 * (n_bytes / n),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+            "config": {"workload": desc, "name": "c3"},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                             "sample": f"first {n} ids; threaded hash recount + sort by key"},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}), flush=True)
+        return
     # per-step budget so that the whole run ends within a few minutes
     budget_s = 150.0
     per_step = budget_s / max(args.steps + args.warmup, 1)
@@ -182,6 +207,76 @@ def run_reference_arm(args, wl):
                                    f"costs the recount up to 8x more per token than the first merges at full size)"},
         "e2e": {"value": value, "unit": "merges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- count-only workload
+def run_count_bench(args, wl, dev):
+    """Initial pair-count microbenchmark on an id stream (16-bit vocabulary): every step loads the
+    resident ids again (pack, untimed) and runs one full histogram pass.  `value` is GB/s at 4 bytes
+    per token over the histogram kernel; the time to move the directly indexed counters into the pair
+    table is reported beside it."""
+    import torch
+    from supertoken_b200 import synth
+    from supertoken_b200.engine import Engine
+    gen, n_tokens, seed, _, desc = wl
+    K, W = args.steps, max(args.warmup, 1)
+    ids, off = synth.config3_ids(n_tokens, seed=seed, device=str(dev))
+    torch.cuda.synchronize()
+    off_np = off.cpu().numpy()
+    slots = 1 << max(20, int(np.ceil(np.log2(max(n_tokens // 4, 1)))))
+    eng = Engine(n_tokens, base_vocab=65536, max_merges=1, device=dev, table_slots=slots)
+    sampler = ClockSampler(dev.index)
+    ms, conv, call = [], [], []
+    for it in range(W + K):
+        eng.reset()
+        eng.append_ids(ids, off_np)
+        torch.cuda.synchronize()
+        if it == W:
+            sampler.start()
+        t = time.perf_counter()
+        eng.count_initial()
+        torch.cuda.synchronize()
+        if it >= W:
+            st = eng.state()
+            call.append((time.perf_counter() - t) * 1e3)
+            ms.append(float(st.count_kernel_ms))
+            conv.append(float(st.count_convert_ms))
+    clocks = sampler.stop()
+    st = eng.state()
+    key, count, ties = eng.select_best(True)
+    peak, peak_kind = peaks()
+    med = float(np.median(ms))
+    gbs = 4.0 * n_tokens / (med / 1e3) / 1e9
+    # end to end: pinned host ids -> device -> pack -> histogram -> best pair back on the host
+    host = torch.empty(n_tokens, dtype=torch.int32, pin_memory=True)
+    host.copy_(ids)
+    del ids
+    torch.cuda.empty_cache()
+    torch.cuda.synchronize()
+    t = time.perf_counter()
+    eng.reset()
+    eng.append_ids(host, off_np)
+    eng.count_initial()
+    k2, c2, _ = eng.select_best(False)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t
+    assert (k2, c2) == (key, count)
+    line = {
+        "metric": "pair_count_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": med, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int32", "data": "synthetic",
+        "config": {"workload": desc, "name": "c3", "tokens": n_tokens, "rows": len(off_np) - 1,
+                   "distinct_pairs": int(st.table_keys), "best_pair": [int(key >> 32), int(key & 0xFFFFFFFF), int(count)],
+                   "l2": "inputs larger than L2", "bytes_per_token": 4},
+        "roofline": {"bound": "hbm", "kernel": "count_dense32_kernel" if med and conv and conv[0] > 0 else "count_kernel",
+                     "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak,
+                     "frac_of_8tbs": gbs / 8000.0, "kernel_ms": med, "to_pair_table_ms": float(np.median(conv)),
+                     "call_ms": float(np.median(call)), "traffic": None},
+        "e2e": {"value": 4.0 * n_tokens / e2e_s / 1e9, "unit": "GB/s", "seconds": e2e_s,
+                "h2d_bytes_per_step": 4.0 * n_tokens + off_np.nbytes, "d2h_bytes_per_step": 24.0},
+        "gpu_launches": 2 * K, "clocks": clocks, "cpu_baseline": None,
     }
     print(json.dumps(line), flush=True)
 
@@ -224,6 +319,10 @@ def main():
 
     from supertoken_b200 import GPUBPETrainer, synth
     from supertoken_b200.engine import Engine
+
+    if args.workload == "c3":
+        run_count_bench(args, wl, dev)
+        return
 
     K, W = args.steps, args.warmup
     corpus = getattr(synth, gen)(n_bytes=n_bytes, seed=seed, device=str(dev))
@@ -328,7 +427,7 @@ def main():
         "e2e": {"value": e2e, "unit": "merges/s", "seconds": e2e_s,
                 "h2d_bytes_per_step": (n_tokens + off_np.nbytes) / max(len(learned), 1),
                 "d2h_bytes_per_step": 24.0},
-        "gpu_launches": 5 * done + 1,
+        "gpu_launches": 4 * done + 1,
         "clocks": clocks,
         "cpu_baseline": cpu,
     }

@@ -61,6 +61,8 @@ typedef struct stbpe_state {
     int64_t repacks;          /* dense re-packs of the stream so far */
     int64_t work_tiles;       /* tiles visited by the last merge (after the pair filter) */
     double count_kernel_ms;   /* device time of the histogram kernel(s) of the last count */
+    double count_convert_ms;  /* 16-bit-vocabulary path only: device time of moving the directly
+                                 indexed counters into the pair table (0 otherwise) */
 } stbpe_state;
 
 /* Lifetime.  Replaces GPUBPETrainer's per-fit device contexts and workspaces

@@ -32,6 +32,8 @@ struct stbpe_engine {
     size_t merge_smem, count_smem;
     bool recs_stale, counted;
     u64 *dense;           // 65 536 global counters of the byte-level count path
+    unsigned int *big;    // 2^32 directly indexed counters of the 16-bit-vocabulary count path (lazy)
+    i64 dense32_min;      // streams shorter than this use the general kernel
     bool only_bytes;      // every token so far came from stbpe_append_bytes (ids < 256)
     ncclComm_t comm;      // own NCCL communicator for the native multi-GPU round loop
     i64 *all_cands;       // world x 4 gathered candidates (native loop)
@@ -40,6 +42,7 @@ struct stbpe_engine {
     void *mail_mapped[STBPE_MAX_PEERS];    // peers' mailboxes as mapped into this process
     bool peers_open;
     float count_ms;       // device time of the histogram kernels of the last count
+    float convert_ms;     // device time of moving a dense histogram into the pair table (wide path)
     cudaEvent_t ev0, ev1;
     uint32_t *tiles_alt;  // second stream buffer of the re-pack (at creation when memory allows)
     i64 *rp_lens, *rp_offs;  // re-pack scratch: tile lengths and their exclusive sums
@@ -161,10 +164,14 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->rp_tmp_bytes = 0;
     e->repacks = 0;
     e->count_ms = 0.f;
+    e->convert_ms = 0.f;
     e->ev0 = e->ev1 = nullptr;
     e->comm = nullptr;
     e->all_cands = nullptr;
     e->own_boxes = false;
+    e->big = nullptr;
+    e->dense32_min = 1ll << 24;
+    if (const char *v = getenv("STBPE_DENSE32_MIN_TOKENS")) e->dense32_min = atoll(v);
     e->mail_own = nullptr;
     memset(e->mail_mapped, 0, sizeof(e->mail_mapped));
     e->peers_open = false;
@@ -413,6 +420,7 @@ static int rebuild_presence(stbpe_engine *e, cudaStream_t s) {
 
 static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
     const bool fresh = e->recs_stale;
+    e->convert_ms = 0.f;
     int rc = prepare_stream_state(e, s);
     if (rc != STBPE_OK) return rc;
     if (fresh) {
@@ -457,6 +465,48 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
         derr &= ~STBPE_DERR_DENSE_OVERFLOW;
         CK(cudaMemcpyAsync(&e->d.st->error, &derr, sizeof(derr), cudaMemcpyHostToDevice, s));
         CK(cudaStreamSynchronize(s));
+    }
+    if (e->d.n_tiles > 0 && fresh && !mg && !e->only_bytes && e->cfg.base_vocab <= 65536 &&
+        e->n_tokens >= e->dense32_min && !getenv("STBPE_NO_DENSE_COUNT")) {
+        // 16-bit vocabulary: directly indexed 32-bit counters in HBM (16 GiB, kept for later counts)
+        const size_t big_bytes = (size_t)4 << 32;
+        if (!e->big) {
+            size_t free_b = 0, total_b = 0;
+            CK(cudaMemGetInfo(&free_b, &total_b));
+            if (free_b > big_bytes + ((size_t)4 << 30)) {
+                cudaError_t c = dev_alloc(e, &e->big, (size_t)1 << 32);
+                if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc dense pair counters");
+                CK(cudaMemsetAsync(e->big, 0, big_bytes, s));
+            }
+        }
+        if (e->big) {
+            CK(cudaMemsetAsync(e->dense, 0, 65536 * sizeof(u64), s));
+            CK(cudaEventRecord(e->ev0, s));
+            CK(cudaFuncSetAttribute(count_dense32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
+            count_dense32_kernel<<<e->sm_count, STBPE_DENSE_THREADS, 32768 * 4, s>>>(e->d, e->n_tokens, e->dense, e->big);
+            CK(cudaGetLastError());
+            CK(cudaEventRecord(e->ev1, s));
+            unsigned int derr = 0;
+            CK(cudaMemcpyAsync(&derr, &e->d.st->error, sizeof(derr), cudaMemcpyDeviceToHost, s));
+            CK(cudaStreamSynchronize(s));
+            if (!(derr & STBPE_DERR_DENSE_OVERFLOW)) {
+                CK(cudaEventElapsedTime(&e->count_ms, e->ev0, e->ev1));
+                CK(cudaEventRecord(e->ev0, s));
+                dense_to_table_kernel<false><<<256, 256, 0, s>>>(e->d, e->dense);
+                CK(cudaGetLastError());
+                dense32_to_table_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, e->big);
+                CK(cudaGetLastError());
+                CK(cudaEventRecord(e->ev1, s));
+                CK(cudaEventSynchronize(e->ev1));
+                CK(cudaEventElapsedTime(&e->convert_ms, e->ev0, e->ev1));
+                return STBPE_OK;
+            }
+            // an id of 65 536 or more: discard what was counted and use the general kernel
+            derr &= ~STBPE_DERR_DENSE_OVERFLOW;
+            CK(cudaMemcpyAsync(&e->d.st->error, &derr, sizeof(derr), cudaMemcpyHostToDevice, s));
+            CK(cudaMemsetAsync(e->big, 0, big_bytes, s));
+            CK(cudaStreamSynchronize(s));
+        }
     }
     if (e->d.n_tiles > 0) {
         int grid = e->count_grid < e->d.n_tiles ? e->count_grid : e->d.n_tiles;
@@ -791,6 +841,7 @@ STBPE_VISIBLE int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *strea
     out->repacks = e->repacks;
     out->work_tiles = h.n_work;
     out->count_kernel_ms = e->count_ms;
+    out->count_convert_ms = e->convert_ms;
     return STBPE_OK;
 }
 

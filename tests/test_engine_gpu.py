@@ -348,6 +348,45 @@ def test_byte_level_dense_count_path(kind):
     e.close()
 
 
+@pytest.mark.parametrize("kind", ["zipf", "too_large_id", "short_rows"])
+def test_wide_dense_count_path_for_16_bit_vocabularies(kind, monkeypatch):
+    # a fresh id stream with base_vocab <= 65 536 is counted into 2^32 directly indexed 32-bit
+    # counters (plus the shared-memory counters for ids below 256); an id of 65 536 or more makes
+    # the engine fall back to the general kernel.  Either way the histogram equals the oracle's,
+    # a second count on the same engine (counters left clean by the first) agrees, and merges follow.
+    monkeypatch.setenv("STBPE_DENSE32_MIN_TOKENS", "1")
+    free, _ = torch.cuda.mem_get_info()
+    if free < (24 << 30):
+        pytest.skip("needs 16 GiB for the counters")
+    if kind == "short_rows":
+        rng = np.random.default_rng(5)
+        ids = rng.integers(0, 65536, 100_003).astype(np.int32)
+        ids[::7] = 5
+        ids[1::7] = 9
+        off = np.sort(np.concatenate([[0, len(ids)], rng.choice(len(ids), 30_000, replace=False)])).astype(np.int64)
+        off = np.unique(off)
+    else:
+        ids, off = synth.config3_ids(1 << 20, seed=2)
+        ids, off = np.asarray(ids).copy(), np.asarray(off)
+        if kind == "too_large_id":
+            ids[12345] = 70000
+    e = Engine(len(ids), base_vocab=65536, max_merges=6, table_slots=1 << 21)
+    for _ in range(2):
+        e.reset()
+        e.append_ids(ids, off)
+        e.count_initial()
+        ok, oc = O.count_pairs_flat(ids, off, 1)
+        k, c = _hist(e)
+        assert np.array_equal(k, ok) and np.array_equal(c, oc)
+        st = e.state()
+        assert (st.count_convert_ms > 0) == (kind != "too_large_id")
+    e.train(6)
+    om, ocnt, _ = O.train_flat(ids.copy(), off.copy(), 65536, 6, 1)
+    m, cnt, _ = e.merges()
+    assert m == om and cnt.tolist() == ocnt
+    e.close()
+
+
 def test_full_size_properties_on_a_256_mib_corpus():
     # at a size the oracle cannot recount merge by merge: (i) the first merges equal the oracle's on
     # the whole corpus, (ii) after several hundred merges (re-packs and tile skipping included) the
