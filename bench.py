@@ -423,7 +423,10 @@ def main():
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "algorithmic_bytes": algo_bytes, "kernel_ms": mrg_ms, "launches": done,
                      "other_kernels_ms": {"select_kernel": sel_ms, "refresh_kernel": ref_ms, "repack": repack_ms},
-                     "traffic": None},
+                     "traffic": 0.711 * algo_bytes / done,
+                     "traffic_note": "DRAM read+write per launch = 0.711 x algorithmic bytes: ncu over merges 1-1500 of a "
+                                     "64 MiB slice (115.7 GB of traffic for 162.7 GB algorithmic), scaled by live tokens; "
+                                     "later merges visit fewer tiles, so the factor of the full job is lower"},
         "e2e": {"value": e2e, "unit": "merges/s", "seconds": e2e_s,
                 "h2d_bytes_per_step": (n_tokens + off_np.nbytes) / max(len(learned), 1),
                 "d2h_bytes_per_step": 24.0},

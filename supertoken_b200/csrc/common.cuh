@@ -27,7 +27,7 @@
 #define STBPE_IDMASK 0x7FFFFFFFu
 #define STBPE_EMPTY 0xFFFFFFFFFFFFFFFFull
 #define STBPE_BLK 256
-#define STBPE_PROWS 8192  // rows of the pair filter: pair keys are hashed onto them (two hashes)
+#define STBPE_PROWS 16384  // rows of the pair filter: pair keys are hashed onto them (three hashes)
 #define STBPE_MAX_PROBE (1u << 20)
 
 // device error bits
@@ -109,7 +109,7 @@ struct EngineDev {
     unsigned int n_blocks;
     // presence[r][w]: bit t of word w of row r says "a pair whose key hashes to r may start in tile
     // 32*w + t" (the tile of the pair's left token; set when such a pair comes into being, never
-    // cleared until the next re-pack).  A Bloom filter with two hashes per pair: false positives
+    // cleared until the next re-pack).  A Bloom filter with three hashes per pair: false positives
     // cost a wasted visit, never a missed one.  Row STBPE_PROWS is a wildcard: tiles that every
     // merge visits because the pair that starts at their last token is not known exactly (their
     // last token is the result of a run of equal tokens that ran on into the next tile).
@@ -277,21 +277,27 @@ __device__ __forceinline__ unsigned int hash32(u64 key) {
     return h;
 }
 
-// pair filter: the two rows of a pair key, and setting the pair's bits for a tile
-__device__ __forceinline__ void filter_rows(u64 key, unsigned int &r1, unsigned int &r2) {
-    const unsigned int h = hash32(key);
-    r1 = h & (STBPE_PROWS - 1);
-    r2 = (h >> 16) & (STBPE_PROWS - 1);
+// pair filter: the three rows of a pair key, and setting the pair's bits for a tile.  With about a
+// thousand distinct pairs in a full tile, three bits per pair over 16 384 rows leave a row about 17 %
+// full and let through about 0.5 % of the tiles that do not hold the pair (two bits over 8 192 rows
+// let through 5 %, which late in a run was most of the tiles a merge visited).
+__device__ __forceinline__ void filter_rows(u64 key, unsigned int &r1, unsigned int &r2, unsigned int &r3) {
+    const u64 h = mix64(key);
+    r1 = (unsigned int)h & (STBPE_PROWS - 1);
+    r2 = (unsigned int)(h >> 20) & (STBPE_PROWS - 1);
+    r3 = (unsigned int)(h >> 40) & (STBPE_PROWS - 1);
 }
 __device__ __forceinline__ void filter_set(const EngineDev &e, int tile, u64 key) {
     if (tile < 0) return;
-    unsigned int r1, r2;
-    filter_rows(key, r1, r2);
+    unsigned int r1, r2, r3;
+    filter_rows(key, r1, r2, r3);
     const unsigned int w = (unsigned int)tile >> 5, bit = 1u << (tile & 31);
     unsigned int *p1 = e.presence + (size_t)r1 * e.presence_words + w;
     unsigned int *p2 = e.presence + (size_t)r2 * e.presence_words + w;
+    unsigned int *p3 = e.presence + (size_t)r3 * e.presence_words + w;
     if (!(*(volatile unsigned int *)p1 & bit)) atomicOr(p1, bit);
     if (!(*(volatile unsigned int *)p2 & bit)) atomicOr(p2, bit);
+    if (!(*(volatile unsigned int *)p3 & bit)) atomicOr(p3, bit);
 }
 
 // slow path: probe for the key, claim an empty slot, or give up after a few probes

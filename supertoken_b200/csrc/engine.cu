@@ -412,7 +412,9 @@ static int rebuild_presence(stbpe_engine *e, cudaStream_t s) {
     clear_skip_state_kernel<<<1, 1, 0, s>>>(e->d);
     CK(cudaGetLastError());
     if (e->d.n_tiles > 0) {
-        presence_rebuild_kernel<<<e->sm_count * 2, 1024, 0, s>>>(e->d);
+        CK(cudaFuncSetAttribute(presence_rebuild_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                STBPE_PROWS * (int)sizeof(unsigned int)));
+        presence_rebuild_kernel<<<e->sm_count * 2, 1024, STBPE_PROWS * sizeof(unsigned int), s>>>(e->d);
         CK(cudaGetLastError());
     }
     return STBPE_OK;

@@ -493,17 +493,18 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
 // starts there) or if its first token is the partner of a head that ends the tile before it.  The
 // pair filter records, per tile, which pairs start in it (including the pair formed by its last
 // token and the first token of the next non-empty tile), so
-//     visit tile t  iff  filter row1(a,b)[t] and filter row2(a,b)[t].
+//     visit tile t  iff  all three filter rows of (a,b) have bit t set.
 // A partner in a tile that is not visited is dropped by the warp that owns the head (fix-up in the
 // merge kernel).  This kernel builds the bitmap of visited tiles and the compact worklist.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
     DevState *st = e.st;
     if (st->stopped || st->exchange_only) return;
-    unsigned int r1, r2;
-    filter_rows(((u64)(uint32_t)st->cur_a << 32) | (u64)(uint32_t)st->cur_b, r1, r2);
+    unsigned int r1, r2, r3;
+    filter_rows(((u64)(uint32_t)st->cur_a << 32) | (u64)(uint32_t)st->cur_b, r1, r2, r3);
     const unsigned int *row1 = e.presence + (size_t)r1 * e.presence_words;
     const unsigned int *row2 = e.presence + (size_t)r2 * e.presence_words;
+    const unsigned int *row3 = e.presence + (size_t)r3 * e.presence_words;
     const unsigned int *wild = e.presence + (size_t)STBPE_PROWS * e.presence_words;
     const int n_words = (e.n_tiles + 31) / 32;
     const int lane = threadIdx.x & 31;
@@ -511,7 +512,7 @@ __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
         const int w = w0 + threadIdx.x;
         unsigned int c = 0;
         if (w < n_words) {
-            c = (row1[w] & row2[w]) | wild[w];
+            c = (row1[w] & row2[w] & row3[w]) | wild[w];
             const int rem = e.n_tiles - w * 32;
             if (rem < 32) c &= (1u << rem) - 1u;
             e.cand_bits[w] = c;
@@ -540,7 +541,7 @@ __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
 // 32 consecutive tiles, i.e. one word of every row: it collects the bits in shared memory and then
 // writes the STBPE_PROWS words with plain stores.
 __global__ void __launch_bounds__(1024) presence_rebuild_kernel(EngineDev e) {
-    __shared__ unsigned int s_rows[STBPE_PROWS];
+    extern __shared__ unsigned int s_rows[];  // STBPE_PROWS words
     const int n_groups = (e.n_tiles + 31) / 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
@@ -564,10 +565,11 @@ __global__ void __launch_bounds__(1024) presence_rebuild_kernel(EngineDev e) {
                 for (int i = lane; i < r.len; i += 32) {
                     const uint32_t t1 = (i + 1 < r.len) ? g[i + 1] : nxt0;
                     if (t1 & STBPE_FLAG) continue;  // not a countable pair
-                    unsigned int r1, r2;
-                    filter_rows(((u64)(g[i] & STBPE_IDMASK) << 32) | (u64)t1, r1, r2);
+                    unsigned int r1, r2, r3;
+                    filter_rows(((u64)(g[i] & STBPE_IDMASK) << 32) | (u64)t1, r1, r2, r3);
                     atomicOr(&s_rows[r1], 1u << warp);
                     atomicOr(&s_rows[r2], 1u << warp);
+                    atomicOr(&s_rows[r3], 1u << warp);
                 }
             }
         }
