@@ -147,6 +147,10 @@ class GPUBPETrainer(BaseTrainer):
         self.h2d_events = self.d2h_events = 0
         self.throughput_metrics: dict = {}
         self.table_slots = 0  # 0 = sized from the token count
+        # a process group initialised by the caller (one process per GPU) shards the corpus over the
+        # ranks: every rank passes its own rows to fit() and all ranks learn the same merges
+        self.use_process_group = True
+        self.exchange_entries = 4096  # delta entries per peer and round
         self._engine: Optional[Engine] = None
         self._last_stats: dict = {}
 
@@ -249,6 +253,10 @@ class GPUBPETrainer(BaseTrainer):
         flat: List[Tuple[torch.Tensor, np.ndarray]] = [_flatten_batch(b) for b in batches]
         total = sum(int(ids.numel()) for ids, _ in flat)
         t0 = time.perf_counter()
+        mode = self._sharded_mode()
+        if mode is not None:
+            self._reject_in_sharded_mode(warm_start_merges, checkpoint_interval)
+            return self._fit_sharded(mode, flat, False, log_every, t0)
         eng = self._make_engine(total)
         for ids, off in flat:
             if ids.numel():
@@ -265,6 +273,11 @@ class GPUBPETrainer(BaseTrainer):
         if isinstance(data, np.ndarray):
             data = torch.from_numpy(np.ascontiguousarray(data, dtype=np.uint8))
         t0 = time.perf_counter()
+        mode = self._sharded_mode()
+        if mode is not None:
+            self._reject_in_sharded_mode(None, None)
+            off = Engine._offsets(row_offsets, int(data.numel()))
+            return self._fit_sharded(mode, [(data, off)], True, log_every, t0)
         eng = self._make_engine(data.numel())
         eng.append_bytes(data, row_offsets)
         if not data.is_cuda:
@@ -321,6 +334,9 @@ class GPUBPETrainer(BaseTrainer):
                     if len(got) < n:
                         break
         loop_s = time.perf_counter() - t
+        return self._finalize(eng.state(), reason, timings, events, warm_applied, loop_s, t0, log_every)
+
+    def _finalize(self, st, reason, timings, events, warm_applied, loop_s, t0, log_every) -> dict:
         timings["apply_merge"].record(loop_s)
         self.bytes_d2h += len(self.merges) * 16
         self.d2h_events += 1
@@ -337,7 +353,6 @@ class GPUBPETrainer(BaseTrainer):
                 self.vocab_size += 1
             if log_every and log_every > 0:
                 logger.info("Stopping: no frequent pairs.")
-        st = eng.state()
         self._last_stats = {"live_tokens": int(st.live_tokens), "table_keys": int(st.table_keys),
                             "table_slots": int(st.table_slots), "loop_s": loop_s,
                             "total_s": time.perf_counter() - t0, "stop_reason": int(reason)}
@@ -364,6 +379,96 @@ class GPUBPETrainer(BaseTrainer):
                 "engine": dict(self._last_stats),
             },
         }
+
+    # ------------------------------------------------------------------ several GPUs
+    def _sharded_mode(self) -> Optional[str]:
+        """``"devices"``: this process drives every GPU of ``devices=(...)`` itself
+        (``gpu_tokenizer/bpe_trainer.py:716-731``, rows split over the devices ``:541-576``);
+        ``"ranks"``: one process per GPU, process group initialised by the caller
+        (``docs/performance.md:70-81`` of the reference); ``None``: one GPU."""
+        if len(self.devices) > 1:
+            return "devices"
+        if self.use_process_group:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                return "ranks"
+        return None
+
+    def _reject_in_sharded_mode(self, warm_start_merges, checkpoint_interval) -> None:
+        if warm_start_merges or self._seed_warm_start_merges or self.randomize_ties or checkpoint_interval:
+            raise NotImplementedError("warm start / resume, randomised ties and checkpoint intervals drive the "
+                                      "merge loop from the host and are available on one GPU only")
+
+    def _fit_sharded(self, mode: str, pieces, as_bytes: bool, log_every: int, t0: float) -> dict:
+        """Merge loop over several GPUs: rows stay where they are loaded, pair keys are owned by
+        hash, every round exchanges the deltas of one merge and all ranks commit the same winner
+        (``supertoken_b200/dist.py``).  ``pieces`` = [(flat ids or bytes, row offsets)] in row order."""
+        from . import dist as D
+        timings = {k: StageTiming(k) for k in ("pair_count", "apply_merge", "host_sync")}
+        events: List[dict] = []
+        self.merges, self.merge_counts, self.vocab_size = [], [], self.base_vocab
+
+        def load(engine, lo_row, hi_row):
+            # rows [lo_row, hi_row) of the concatenation of the pieces
+            r0 = 0
+            for data, off in pieces:
+                n = len(off) - 1
+                a, b = max(lo_row - r0, 0), min(hi_row - r0, n)
+                if a < b:
+                    part, poff = data[int(off[a]):int(off[b])], off[a:b + 1] - off[a]
+                    (engine.append_bytes if as_bytes else engine.append_ids)(part, poff)
+                    if not part.is_cuda:
+                        self.bytes_h2d += part.numel() * (1 if as_bytes else 4)
+                        self.h2d_events += 1
+                r0 += n
+
+        lens = np.concatenate([np.diff(off) for _, off in pieces]) if pieces else np.zeros(0, np.int64)
+        goff = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        n_rows = len(goff) - 1
+        t = time.perf_counter()
+        engines: List[Engine] = []
+        closer = None
+        if mode == "devices":
+            world = len(self.devices)
+            cuts = D.shard_rows(goff, world)
+            workers = []
+            for r, dev in enumerate(self.devices):
+                lo, hi = cuts[r]
+                e = Engine(max(int(goff[hi] - goff[lo]), 1), base_vocab=self.base_vocab,
+                           max_merges=max(self.target_merges, 1), device=dev, table_slots=self.table_slots,
+                           world_size=world, rank=r)
+                load(e, lo, hi)
+                engines.append(e)
+                workers.append(D.EngineWorker(e, cap_per_peer=self.exchange_entries))
+            loop = D.ShardedBPE(workers, D.LocalComm())
+        else:
+            import torch.distributed as dist
+            world, rank = dist.get_world_size(), dist.get_rank()
+            e = Engine(max(int(goff[-1]), 1), base_vocab=self.base_vocab, max_merges=max(self.target_merges, 1),
+                       device=torch.device(self.device), table_slots=self.table_slots, world_size=world, rank=rank)
+            load(e, 0, n_rows)
+            engines.append(e)
+            same_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0")) == world
+            driver = os.environ.get("STBPE_MG_DRIVER", "peer" if same_node and world <= 16 else "nccl")
+            loop = D.PeerLoop(e, self.exchange_entries) if driver == "peer" else D.NativeLoop(e, self.exchange_entries)
+            closer = getattr(loop, "close", None)
+        try:
+            timings["pair_count"].record(time.perf_counter() - t)
+            t = time.perf_counter()
+            done, reason = loop.train()
+            loop_s = time.perf_counter() - t
+            got, counts, _ = engines[0].merges(0, done)
+            self.merges = list(got)
+            self.merge_counts = [int(c) for c in counts]
+            self.vocab_size = self.base_vocab + len(self.merges)
+            st = engines[0].state()
+            if closer is not None:
+                closer()
+        finally:
+            for e in engines:
+                e.close()
+        return self._finalize(st, reason, timings, events, 0, loop_s, t0, log_every)
+
 
     def _loop_random_ties(self, eng: Engine, remaining: int) -> int:
         """Host-driven loop for ``randomize_ties``: the seeded ``random.Random`` picks an index

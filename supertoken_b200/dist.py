@@ -186,7 +186,8 @@ class ShardedBPE:
             self._counted = True
             budget -= 1
         while True:
-            done, reason = self.workers[0].progress()
+            states = [w.progress() for w in self.workers]   # every rank may re-pack its own tiles here
+            done, reason = states[0]
             if reason != L.RUNNING or budget <= 0:
                 return done, reason
             n = min(check_every, budget)

@@ -146,3 +146,81 @@ def test_two_gpus_over_nccl_match_oracle(native):
     assert not failed, failed
     for rank, m, cnt, done, stop in results:
         assert m == om and cnt == oc and done == target and stop == L.STOP_TARGET
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_trainer_with_two_devices_in_one_process():
+    # GPUBPETrainer(devices=(...)): the rows are split over the devices, one engine per device, the
+    # exchange is a copy between the devices; merges equal the single-stream oracle
+    from supertoken_b200 import GPUBPETrainer
+    c = synth.config2_mixed(2 << 20, seed=5, lexicon=3000, mean_doc_bytes=1500)
+    target = 70
+    om, oc, _ = O.train_flat(*O.flatten_rows(corpus_rows(c)), 256, target, 1)
+    tr = GPUBPETrainer(base_vocab=256, merges=target, devices=("cuda:0", "cuda:1"))
+    res = tr.fit_bytes(np.asarray(c.data), np.asarray(c.row_offsets))
+    assert res["merges"] == om and tr.merge_counts == oc and res["vocab_size"] == 256 + target
+    # the padded-batch entry point takes the same route
+    rows = corpus_rows(c)[:40]
+    Lmax = max(len(r) for r in rows)
+    tok = torch.full((len(rows), Lmax), -1, dtype=torch.int32)
+    val = torch.zeros((len(rows), Lmax), dtype=torch.uint8)
+    for i, r in enumerate(rows):
+        tok[i, :len(r)] = torch.from_numpy(np.asarray(r, dtype=np.int32))
+        val[i, :len(r)] = 1
+    lens = torch.tensor([len(r) for r in rows], dtype=torch.int32)
+    om2, _, _ = O.train_flat(*O.flatten_rows(rows), 256, 25, 1)
+    tr2 = GPUBPETrainer(base_vocab=256, merges=25, devices=("cuda:0", "cuda:1"))
+    assert tr2.fit([(tok[:20], val[:20], lens[:20]), (tok[20:], val[20:], lens[20:])], log_every=0)["merges"] == om2
+
+
+def _trainer_rank(rank, world, port, target, q):
+    import datetime
+    import torch.distributed as dist
+    from supertoken_b200 import GPUBPETrainer
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), LOCAL_WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
+    try:
+        c = synth.config2_mixed(2 << 20, seed=5, lexicon=3000, mean_doc_bytes=1500)
+        off = np.asarray(c.row_offsets)
+        lo, hi = shard_rows(off, world)[rank]
+        tr = GPUBPETrainer(base_vocab=256, merges=target, device=f"cuda:{rank}")
+        res = tr.fit_bytes(np.asarray(c.data)[off[lo]:off[hi]], off[lo:hi + 1] - off[lo])
+        q.put((rank, res["merges"], tr.merge_counts, res["vocab_size"], 0))
+    except Exception as exc:
+        q.put((rank, "error", repr(exc), 0, 0))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_trainer_in_a_process_group_of_two_ranks():
+    # one process per GPU, process group initialised by the caller: every rank passes its own rows
+    # to the unchanged trainer call and all ranks return the merges of the whole corpus
+    import torch.multiprocessing as mp
+    world, target = 2, 70
+    c = synth.config2_mixed(2 << 20, seed=5, lexicon=3000, mean_doc_bytes=1500)
+    om, oc, _ = O.train_flat(*O.flatten_rows(corpus_rows(c)), 256, target, 1)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_trainer_rank, args=(r, world, port, target, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = []
+    for _ in range(world):
+        results.append(q.get(timeout=240))
+        if results[-1][1] == "error":
+            break
+    failed = [r for r in results if r[1] == "error"]
+    for p in procs:
+        p.join(timeout=5 if failed else 60)
+        if p.is_alive():
+            p.terminate()
+    assert not failed, failed
+    for rank, m, cnt, vocab, _ in results:
+        assert m == om and cnt == oc and vocab == 256 + target
