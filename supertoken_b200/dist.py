@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import List, Optional, Sequence, Tuple
+from typing import Callable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -62,6 +62,62 @@ def shard_rows(row_offsets: np.ndarray, world: int) -> List[Tuple[int, int]]:
         cuts.append(min(max(k, cuts[-1]), n_rows))
     cuts.append(n_rows)
     return [(cuts[r], cuts[r + 1]) for r in range(world)]
+
+
+# ----------------------------------------------------------------------------- reducer hook
+# The reference lets a launcher install the function that sums sparse pair histograms over the
+# ranks (``gpu_tokenizer/dist/launcher.py:25``, ``:98-110``; default ``utils.reduce_pair_histograms``,
+# ``gpu_tokenizer/utils.py:863-978``).  The engine here never ships whole histograms (it exchanges
+# per-merge deltas by key owner), but callers of the hook find the same three names with the same
+# contract: (keys int64[n], counts int64[n]) -> (sorted unique keys, summed counts), identical on
+# every rank.
+ReducerFn = Callable[[torch.Tensor, torch.Tensor], Tuple[torch.Tensor, torch.Tensor]]
+_histogram_reducer: Optional[ReducerFn] = None
+
+
+def register_histogram_reducer(fn: Optional[ReducerFn]) -> None:
+    global _histogram_reducer
+    _histogram_reducer = fn
+
+
+def get_histogram_reducer() -> ReducerFn:
+    return _histogram_reducer if _histogram_reducer is not None else reduce_pair_histograms
+
+
+def _aggregate(keys: torch.Tensor, counts: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    if keys.numel() == 0:
+        return keys.to(torch.int64), counts.to(torch.int64)
+    keys, order = torch.sort(keys.to(torch.int64))
+    uniq, inverse = torch.unique_consecutive(keys, return_inverse=True)
+    out = torch.zeros(uniq.numel(), dtype=torch.int64, device=keys.device)
+    out.index_add_(0, inverse, counts.to(torch.int64)[order])
+    return uniq, out
+
+
+def reduce_pair_histograms(keys: torch.Tensor, counts: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sum sparse histograms over the ranks of the process group (all ranks get the same sorted
+    result); without an initialised group, or with one rank, only duplicate keys are merged."""
+    import torch.distributed as dist
+    keys, counts = _aggregate(keys, counts)
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return keys, counts
+    world = dist.get_world_size(group)
+    n = torch.tensor([keys.numel()], dtype=torch.int64, device=keys.device)
+    sizes = [torch.zeros_like(n) for _ in range(world)]
+    dist.all_gather(sizes, n, group=group)
+    sizes = [int(x.item()) for x in sizes]
+    cap = max(sizes)
+    if cap == 0:
+        return keys, counts
+    pad_k = torch.zeros(cap, dtype=torch.int64, device=keys.device)
+    pad_c = torch.zeros(cap, dtype=torch.int64, device=keys.device)
+    pad_k[:keys.numel()], pad_c[:keys.numel()] = keys, counts
+    all_k = [torch.empty_like(pad_k) for _ in range(world)]
+    all_c = [torch.empty_like(pad_c) for _ in range(world)]
+    dist.all_gather(all_k, pad_k, group=group)
+    dist.all_gather(all_c, pad_c, group=group)
+    return _aggregate(torch.cat([k[:m] for k, m in zip(all_k, sizes)]),
+                      torch.cat([c[:m] for c, m in zip(all_c, sizes)]))
 
 
 # ----------------------------------------------------------------------------- workers

@@ -100,3 +100,58 @@ def test_stop_rules_across_ranks():
         workers = [CpuWorker(rows[r::2], r, 2, 256, 5, 16) for r in range(2)]
         done, stop = ShardedBPE(workers, LocalComm()).train(check_every=2)
         assert done == 0 and stop == expect
+
+
+def _reducer_rank(rank, world, port, q):
+    from supertoken_b200.dist import get_histogram_reducer, register_histogram_reducer
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rows, off = _corpus()
+        lo, hi = shard_rows(off, world)[rank]
+        ids, o2 = O.flatten_rows(rows[lo:hi]) if hi > lo else (np.zeros(0, np.int32), np.zeros(1, np.int64))
+        k, c = O.count_pairs_flat(ids, o2, 1) if hi > lo else (np.zeros(0, np.uint64), np.zeros(0, np.int64))
+        # unsorted input with a duplicated key: the reducer merges duplicates as well
+        keys = torch.from_numpy(np.concatenate([k[::-1], k[:1]]).astype(np.int64))
+        counts = torch.from_numpy(np.concatenate([c[::-1], np.array([5], np.int64)[:len(k[:1])]]))
+        register_histogram_reducer(None)
+        gk, gc = get_histogram_reducer()(keys, counts)
+        q.put((rank, gk.tolist(), gc.tolist(), int(k[0]) if len(k) else -1))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_histogram_reducer_hook_sums_over_gloo_ranks():
+    # mirror of the reference's reducer hook: every rank gets the same sorted global histogram
+    from supertoken_b200.dist import get_histogram_reducer, reduce_pair_histograms, register_histogram_reducer
+    rows, off = _corpus()
+    world = 2
+    gk, gc = O.count_pairs_flat(*O.flatten_rows(rows), 1)
+    want = dict(zip(gk.astype(np.int64).tolist(), gc.tolist()))
+    # a pair that straddles the two shards does not exist (rows are never split), so the sum of the
+    # shard histograms is the histogram of the corpus; each rank added 5 to its first key
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_reducer_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, _, _, first in results:
+        if first >= 0:
+            want[first] += 5
+    for _, keys, counts, _ in results:
+        assert keys == sorted(want) and counts == [want[k] for k in keys]
+    # the hook itself
+    marker = lambda k, c: (k, c)
+    register_histogram_reducer(marker)
+    assert get_histogram_reducer() is marker
+    register_histogram_reducer(None)
+    assert get_histogram_reducer() is reduce_pair_histograms
+    k, c = reduce_pair_histograms(torch.tensor([7, 3, 7]), torch.tensor([1, 2, 4]))   # no group: local merge only
+    assert k.tolist() == [3, 7] and c.tolist() == [2, 5]
