@@ -189,8 +189,15 @@ __device__ __forceinline__ void table_add(const EngineDev &e, u64 key, i64 delta
             }
         }
         if (k == key) {
-            atomicAdd((u64 *)&s->count, (u64)delta);
-            mark_dirty(e, h);
+            const i64 now = (i64)atomicAdd((u64 *)&s->count, (u64)delta) + delta;
+            // The maximum of the slot's block can only change if this key is the recorded maximum or
+            // if its count now reaches it (the add that brings a key to its final count sees that
+            // count, because the adds on one slot are serialised; the recorded maxima do not change
+            // while deltas are applied).  Only those blocks are recomputed by refresh_kernel.
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(e.blockmax + (h / STBPE_BLK)));
+            const u64 mk = ((u64)raw.y << 32) | raw.x;
+            const i64 mc = (i64)(((u64)raw.w << 32) | raw.z);
+            if (key == mk || now > mc || (now == mc && key < mk)) mark_dirty(e, h);
             return;
         }
         h = (h + 1) & e.mask;

@@ -83,26 +83,39 @@ __global__ void clear_table_kernel(EngineDev e) {
 // shared memory as 65 536 16-bit counters (two per 32-bit word, 128 KB).  Each token costs one
 // shared-memory atomic on a direct index: no hashing, no key compare.
 // A 16-bit counter is kept below 2^15: the thread whose add takes it to 0x8000 moves 0x8000 of it
-// to the global 64-bit counter.  Should a counter ever be seen at 0xC000 or above (32 768 further
+// to the global 64-bit counter.  Should a counter ever be seen above 0xC000 (16 384 further
 // adds would have to slip in before that subtraction lands) the kernel raises
 // STBPE_DERR_DENSE_OVERFLOW and the host recounts with the general kernel, so the result is exact
 // or the failure is reported, never silently wrong.
 // ---------------------------------------------------------------------------------------
+// Word of the shared-memory table that holds the counter of a 16-bit key (two counters per word).
+// The bank would be bits 1-5 of the right byte alone, and text concentrates those on a dozen values
+// (lower-case letters, the space), so the low five bits are XOR-ed with the low bits of the left
+// byte: a bijection inside each left-byte row that spreads hot right bytes over the banks.
+__device__ __forceinline__ unsigned int dense_word(unsigned int key) { return (key >> 1) ^ ((key >> 8) & 31u); }
+
+// rare path of dense_add: the add took one of the two 16-bit halves of the word to 0x8000 or beyond
+__device__ __noinline__ void dense_hand_over(unsigned int *s_tab, u64 *g_dense, unsigned int *derr,
+                                             unsigned int key, unsigned int now) {
+    const unsigned int sh = (key & 1u) * 16u;
+    const unsigned int h = (now >> sh) & 0xFFFFu;  // this key's counter after the add
+    if (h == 0x8000u) {
+        atomicSub(&s_tab[dense_word(key)], 0x8000u << sh);
+        atomicAdd(&g_dense[key], 0x8000ull);
+    } else if (h > 0xC000u) {
+        atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
+    }
+    // 0x8000 < h <= 0xC000: another thread is handing this counter over; h < 0x8000: it was the other half
+}
+
 __device__ __forceinline__ void dense_add(unsigned int *s_tab, u64 *g_dense, unsigned int *derr, uint32_t t0,
                                           uint32_t t1) {
-    if (t1 & STBPE_FLAG) return;  // the right token starts a row (or lies past the end)
-    const unsigned int key = ((t0 & 0xFFu) << 8) | t1;
-    const unsigned int sh = (key & 1u) * 16u;
-    const unsigned int old = atomicAdd(&s_tab[key >> 1], 1u << sh);
-    const unsigned int h = (old >> sh) & 0xFFFFu;
-    if (h >= 0x7FFFu) {  // rare
-        if (h == 0x7FFFu) {
-            atomicSub(&s_tab[key >> 1], 0x8000u << sh);
-            atomicAdd(&g_dense[key], 0x8000ull);
-        } else if (h >= 0xC000u) {
-            atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
-        }
-    }
+    if ((int)t1 < 0) return;  // the right token starts a row (or lies past the end): bit 31 set
+    // key = (low byte of t0) << 8 | t1; bytes 1 and 2 of t1 are zero for ids below 256
+    const unsigned int key = __byte_perm(t1, t0, 0x2140);
+    const unsigned int inc = (key & 1u) ? 0x10000u : 1u;
+    const unsigned int now = atomicAdd(&s_tab[dense_word(key)], inc) + inc;
+    if (now & 0x80008000u) dense_hand_over(s_tab, g_dense, derr, key, now);
 }
 
 #define STBPE_DENSE_THREADS 1024
@@ -146,8 +159,9 @@ __global__ void __launch_bounds__(STBPE_DENSE_THREADS, 1)
         }
     }
     __syncthreads();
-    for (int w = threadIdx.x; w < 32768; w += STBPE_DENSE_THREADS) {
-        const unsigned int x = s_tab[w];
+    for (int p = threadIdx.x; p < 32768; p += STBPE_DENSE_THREADS) {
+        const unsigned int x = s_tab[p];
+        const unsigned int w = (unsigned int)p ^ (((unsigned int)p >> 7) & 31u);  // inverse of dense_word
         if (x & 0xFFFFu) atomicAdd(&g_dense[2 * w], (u64)(x & 0xFFFFu));
         if (x >> 16) atomicAdd(&g_dense[2 * w + 1], (u64)(x >> 16));
     }
@@ -214,8 +228,9 @@ __global__ void __launch_bounds__(STBPE_DENSE_THREADS, 1)
         }
     }
     __syncthreads();
-    for (int w = threadIdx.x; w < 32768; w += STBPE_DENSE_THREADS) {
-        const unsigned int x = s_tab[w];
+    for (int p = threadIdx.x; p < 32768; p += STBPE_DENSE_THREADS) {
+        const unsigned int x = s_tab[p];
+        const unsigned int w = (unsigned int)p ^ (((unsigned int)p >> 7) & 31u);  // inverse of dense_word
         if (x & 0xFFFFu) atomicAdd(&g_dense[2 * w], (u64)(x & 0xFFFFu));
         if (x >> 16) atomicAdd(&g_dense[2 * w + 1], (u64)(x >> 16));
     }
@@ -305,10 +320,13 @@ __global__ void refresh_kernel(EngineDev e, int all) {
             Slot s;
             s.key = bk;
             s.count = bc;
+            const Slot was = e.blockmax[blk];
             e.blockmax[blk] = s;
             e.dirty_flag[blk] = 0u;
             const unsigned int sb = blk >> 8;
-            if (!all && atomicExch(&e.dirty2_flag[sb], 1u) == 0u) e.dirty2_list[atomicAdd(&e.st->n_dirty2, 1u)] = sb;
+            // the super-block is recomputed only if this block's maximum really changed
+            if (!all && (was.key != s.key || was.count != s.count) && atomicExch(&e.dirty2_flag[sb], 1u) == 0u)
+                e.dirty2_list[atomicAdd(&e.st->n_dirty2, 1u)] = sb;
         }
     }
 }
