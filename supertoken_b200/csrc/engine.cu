@@ -194,8 +194,11 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     if (e->max_tiles < 1) e->max_tiles = 1;
     u64 slots = cfg->table_slots > 0 ? (u64)cfg->table_slots : (u64)cfg->max_tokens / 4;
     if (cfg->table_slots <= 0) {
+        // keys are never removed, so the table must hold every pair a run ever creates: 2^27 slots
+        // carried 32 000 merges on 2^30 tokens; streams of 2^32 tokens and more get 2^29 (8 GiB)
+        const u64 cap = cfg->max_tokens >= (1ll << 32) ? (1ull << 29) : (1ull << 27);
         if (slots < (1ull << 20)) slots = 1ull << 20;
-        if (slots > (1ull << 27)) slots = 1ull << 27;
+        if (slots > cap) slots = cap;
     }
     slots = next_pow2(slots < (u64)STBPE_BLK ? STBPE_BLK : slots);
     e->slots = slots;
