@@ -1029,7 +1029,7 @@ STBPE_VISIBLE int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev, vo
 // The exchange of a round done by the kernels themselves: every rank owns a mailbox that its peers
 // map through CUDA IPC; drain_peer_kernel stores the deltas into the owners' mailboxes,
 // select_kernel (mode 3) stores the candidate into every mailbox, and apply_peer_kernel /
-// commit_peer_kernel wait (bounded, two seconds) for the senders' flags.  A round is six launches
+// the tail of select_kernel wait (bounded, two seconds) for the senders' flags.  A round is six launches
 // and nothing else, so batches of rounds replay as one CUDA graph.  One rank per GPU only.
 STBPE_VISIBLE int stbpe_mg_peer_export(stbpe_engine *e, int64_t cap_per_peer, void *handle_out64) {
     if (!e || !handle_out64 || cap_per_peer < 1) return STBPE_E_BADARG;
@@ -1105,9 +1105,7 @@ static int enqueue_peer_round(stbpe_engine *e, bool count_round, cudaStream_t s)
     CK(cudaGetLastError());
     rc = launch_refresh(e, 0, s);
     if (rc != STBPE_OK) return rc;
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 3, 0, e->cand);
-    CK(cudaGetLastError());
-    commit_peer_kernel<<<1, 32, 0, s>>>(e->d, e->cfg.max_merges);
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 3, 0, e->cand, e->cfg.max_merges);
     CK(cudaGetLastError());
     return STBPE_OK;
 }

@@ -421,9 +421,10 @@ __device__ __forceinline__ void block_best(u64 &bk, i64 &bc, u64 *s_k, i64 *s_c)
 #include "peer_kernels.cuh"
 
 // mode 0: peek (result into the state); 1: single rank, advance or stop; 2: candidate of this rank
-// into cand; 3: candidate of this rank into every peer mailbox
+// into cand; 3: candidate of this rank into every peer mailbox, then wait for the peers' candidates
+// and commit (target = the merge target of the engine)
 __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
-    select_kernel(EngineDev e, int mode, int all2, i64 *cand) {
+    select_kernel(EngineDev e, int mode, int all2, i64 *cand, int target = 0) {
     DevState *st = e.st;
     if (mode == 1 && st->stopped) return;
     __shared__ u64 s_k[STBPE_SELECT_THREADS / 32];
@@ -503,6 +504,7 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
         cand[3] = 0;
     } else {
         publish_candidate(e, bk, bc, st->round_incomplete);
+        commit_from_mailbox(e, target);
     }
 }
 

@@ -4,7 +4,7 @@
 // host step inside a round, so a batch of rounds is one CUDA graph.
 //
 // Why the waits cannot deadlock and chunks cannot be overwritten while in use: a rank's stream runs
-// drain(r) -> apply(r) -> select(r) -> commit(r) -> drain(r+1).  Nothing before drain(r) waits for a
+// drain(r) -> apply(r) -> select+commit(r) -> drain(r+1).  Nothing before drain(r) waits for a
 // peer's round-r data, so every rank reaches its round-r sends once its round r-1 is over.  A peer
 // writes my inbox chunk for round r+1 only after its commit(r), which waited for my candidate of
 // round r, which I published after my apply(r) had finished reading the chunk; it writes my
@@ -121,11 +121,13 @@ __global__ void apply_peer_kernel(EngineDev e) {
     if ((int)threadIdx.x < e.world) {
         if (!peer_wait(&own->inbox_flag[threadIdx.x], round, st)) s_ok = 0;
     }
+    __shared__ i64 s_n[STBPE_MAX_PEERS];
+    if ((int)threadIdx.x < e.world && s_ok) s_n[threadIdx.x] = (i64)__ldcg(&mail_chunk(e, e.rank, threadIdx.x)[0].key);
     __syncthreads();
     if (!s_ok) return;
     for (int p = 0; p < e.world; ++p) {
         const Slot *chunk = mail_chunk(e, e.rank, p);
-        i64 n = (i64)__ldcg(&chunk[0].key);
+        i64 n = s_n[p];
         if (n > e.cap_per_peer) {
             n = e.cap_per_peer;
             if (blockIdx.x == 0 && threadIdx.x == 0) st->round_incomplete = 1;
@@ -138,7 +140,8 @@ __global__ void apply_peer_kernel(EngineDev e) {
 }
 
 // This rank's candidate {key, count, incomplete, 0} into every mailbox (called by the one thread
-// that finishes select_kernel).
+// that finishes select_kernel, which then commits with commit_from_mailbox: publishing comes before
+// any wait on every rank, so the waits cannot block one another).
 __device__ __forceinline__ void publish_candidate(const EngineDev &e, u64 key, i64 count, i64 incomplete) {
     const u64 round = *(volatile u64 *)&mail_header(e, e.rank)->round + 1;
     for (int p = 0; p < e.world; ++p) {
@@ -154,32 +157,31 @@ __device__ __forceinline__ void publish_candidate(const EngineDev &e, u64 key, i
 }
 
 // Every rank waits for all candidates of the round and takes the same decision (commit_kernel's
-// rule); the round counter advances whatever the decision.
-__global__ void commit_peer_kernel(EngineDev e, int target) {
-    __shared__ int s_ok;
+// rule); the round counter advances whatever the decision.  Called by one thread.
+__device__ __forceinline__ void commit_from_mailbox(const EngineDev &e, int target) {
     DevState *st = e.st;
     MailHeader *own = mail_header(e, e.rank);
     const u64 round = *(volatile u64 *)&own->round + 1;
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncwarp();
-    if ((int)threadIdx.x < e.world) {
-        if (!peer_wait(&own->cand_flag[threadIdx.x], round, st)) s_ok = 0;
-    }
-    __syncwarp();
-    if (threadIdx.x != 0) return;
-    __threadfence_system();
+    bool ok = true;
+    for (int p = 0; p < e.world; ++p) ok &= peer_wait(&own->cand_flag[p], round, st);
     own->round = round;
     st->target = target;
     st->round_incomplete = 0;
-    if (!s_ok || st->stopped) return;
+    if (!ok || st->stopped) return;
     u64 bk = STBPE_EMPTY;
     i64 bc = 0;
     bool incomplete = false;
+    i64 c[STBPE_MAX_PEERS][3];
+#pragma unroll 1
+    for (int r = 0; r < e.world; ++r) {  // all loads first, then the comparison chain
+        c[r][0] = __ldcg(&own->cands[r][0]);
+        c[r][1] = __ldcg(&own->cands[r][1]);
+        c[r][2] = __ldcg(&own->cands[r][2]);
+    }
     for (int r = 0; r < e.world; ++r) {
-        const i64 *c = own->cands[r];
-        const u64 k = (u64)__ldcg(c);
-        const i64 n = __ldcg(c + 1);
-        incomplete |= __ldcg(c + 2) != 0;
+        const u64 k = (u64)c[r][0];
+        const i64 n = c[r][1];
+        incomplete |= c[r][2] != 0;
         if (n > 0 && better(k, n, bk, bc)) {
             bk = k;
             bc = n;

@@ -398,7 +398,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     if os.environ.get("STBPE_MG_PYTHON_ROUNDS"):
         driver = "python"
     native = driver != "python"
-    launches_per_round = {"peer": 7, "nccl": 7, "python": 7}[driver]
+    launches_per_round = {"peer": 6, "nccl": 7, "python": 7}[driver]
 
     def make(max_merges):
         e = Engine(max(n_local, 1), base_vocab=256, max_merges=max(max_merges, 1), device=dev,

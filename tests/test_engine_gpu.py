@@ -161,6 +161,27 @@ def test_config1_slice_full_parity():
     _check_against_oracle([r for r in corpus_rows(c)], 256, 150)
 
 
+def test_config1_full_size_parity():
+    # the reference's CPU-runnable configuration at its full size: 16 MiB, 16 rows of 1 MiB,
+    # 1 000 merges; merge list, counts and final histogram bit-exact against the oracle
+    c = synth.config1_text(16 << 20, seed=0)
+    data, off = np.asarray(c.data), np.asarray(c.row_offsets)
+    assert len(off) - 1 == 16
+    e = Engine(len(data), base_vocab=256, max_merges=1000)
+    e.append_bytes(data, off)
+    e.count_initial()
+    e.train(1000)
+    m, cnt, _ = e.merges()
+    ids = data.astype(np.int32)
+    o2 = off.astype(np.int64).copy()
+    om, oc, reason = O.train_flat(ids, o2, 256, 1000, 1, copy=False)   # leaves the merged stream in ids / o2
+    assert m == om and cnt.tolist() == oc and len(m) == 1000
+    ok, okc = O.count_pairs_flat(ids[:o2[-1]].copy(), o2, 1)
+    k, kc = _hist(e)
+    assert np.array_equal(k, ok) and np.array_equal(kc, okc)
+    e.close()
+
+
 def test_config5_slice_full_parity():
     c = synth.config5_adversarial(3 << 20, seed=4)
     _check_against_oracle([r for r in corpus_rows(c)], 256, 120)
