@@ -178,9 +178,9 @@ def run_reference_arm(args, wl):
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}), flush=True)
         return
-    # per-step budget so that the whole run ends within a few minutes
-    budget_s = 150.0
-    per_step = budget_s / max(args.steps + args.warmup, 1)
+    # time per step such that the whole run ends within a few minutes
+    total_s = 150.0
+    per_step = total_s / max(args.steps + args.warmup, 1)
     probe = getattr(synth, gen)(n_bytes=1 << 20, seed=seed)
     ids, off = cpu_sample(np.asarray(probe.data), np.asarray(probe.row_offsets), 1 << 20)
     t, cores = time_oracle(ids, off, 3, 0)

@@ -236,20 +236,20 @@ class ShardedBPE:
         is applied by one more round before the target stop is raised.  Returns (merges committed,
         stop reason) as every rank sees them; the host reads device state only every
         ``check_every`` rounds."""
-        budget = max_rounds if max_rounds is not None else 1 << 62
+        left = max_rounds if max_rounds is not None else 1 << 62
         if not self._counted:
             self._round(True)
             self._counted = True
-            budget -= 1
+            left -= 1
         while True:
             states = [w.progress() for w in self.workers]   # every rank may re-pack its own tiles here
             done, reason = states[0]
-            if reason != L.RUNNING or budget <= 0:
+            if reason != L.RUNNING or left <= 0:
                 return done, reason
-            n = min(check_every, budget)
+            n = min(check_every, left)
             for _ in range(n):
                 self._round(False)
-            budget -= n
+            left -= n
 
 
 class NativeLoop:
