@@ -75,7 +75,7 @@ struct DevState {
     unsigned int n_dirty2;     // super-blocks whose maximum must be recomputed
     unsigned int pad1;
     int n_work;                // tiles on this merge's worklist; < 0 = every tile
-    int filter_stale;          // (unused) visit every tile
+    int pad3;
     unsigned int n_fixups;     // partners dropped in a tile the merge did not visit (statistics)
     int pad2;
     int exchange_only;         // multi-GPU: deltas still in flight, the next round only exchanges

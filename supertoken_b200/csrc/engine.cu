@@ -406,7 +406,6 @@ static int prepare_stream_state(stbpe_engine *e, cudaStream_t s) {
 }
 
 __global__ void clear_skip_state_kernel(EngineDev e) {
-    e.st->filter_stale = 0;
     e.st->n_work = 0;  // a merge that is committed but not yet applied builds its worklist from here
 }
 

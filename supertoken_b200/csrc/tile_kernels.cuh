@@ -18,9 +18,6 @@
 #pragma once
 #include "common.cuh"
 
-#ifndef STBPE_DBG
-#define STBPE_DBG 0
-#endif
 #define STBPE_DERR_TIMEOUT 32u
 #define STBPE_SPIN_LIMIT (1u << 20)
 #define STBPE_NCW 8                              // consumer warps per CTA
@@ -530,7 +527,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                 continue;
             }
             const int newlen = base;
-            if (!(STBPE_DBG & 8)) fence_async_smem();  // the bulk store reads these writes through the async proxy
+            fence_async_smem();  // the bulk store reads these writes through the async proxy
             __syncwarp();
             if (same && last_head && lane == 0) {
                 // the run of a's goes on in the next tile: the pair that will start at the collapsed
@@ -558,7 +555,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                 }
             }
             if (lane == 0) {
-                if (newlen > 0 && !(STBPE_DBG & 1)) {
+                if (newlen > 0) {
                     tma_store_1d(e.tiles + (i64)tile * STBPE_TILE, s_tok, ((uint32_t)newlen * 4u + 15u) & ~15u);
                     tma_commit();
                     pending = stage;
@@ -572,7 +569,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                 dst->tail2 = newlen > 1 ? s_tok[newlen - 2] : STBPE_NONE;
                 dst->ver = m;
                 removed += len - newlen;
-                if (newlen == 0 || (STBPE_DBG & 1)) mbar_arrive(&pipe.empty[stage]);
+                if (newlen == 0) mbar_arrive(&pipe.empty[stage]);
             }
         }
         drain_queue<MG>(pipe.tab, e, a, b, nw, queue, qn, lane);
