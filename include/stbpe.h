@@ -205,6 +205,11 @@ int stbpe_mg_peer_export(stbpe_engine *e, int64_t cap_per_peer, void *handle_out
 int stbpe_mg_peer_open(stbpe_engine *e, const void *handles, int32_t n_handles);
 int stbpe_mg_peer_run(stbpe_engine *e, int first, int n_rounds, void *stream);
 int stbpe_mg_peer_close(stbpe_engine *e);
+/* Ranks of one process (one GPU each, peer access enabled by the caller) skip CUDA IPC:
+ *   stbpe_mg_peer_mailbox : this rank's mailbox as a device pointer (after stbpe_mg_peer_export)
+ *   stbpe_mg_peer_set     : the mailboxes of all ranks as device pointers, indexed by rank. */
+int stbpe_mg_peer_mailbox(stbpe_engine *e, void **out);
+int stbpe_mg_peer_set(stbpe_engine *e, const void *const *mailboxes, int32_t n);
 
 /* Stateless operators on padded [B, L] batches resident on the device, with the
  * reference's operator signatures.

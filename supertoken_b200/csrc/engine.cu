@@ -380,7 +380,7 @@ static int check_device_error(stbpe_engine *e, cudaStream_t s) {
         return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (pair table full)");
     if (err & STBPE_DERR_OUTBOX_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (delta outbox full)");
     if (err & STBPE_DERR_LTABLE_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (local delta table full)");
-    if (err & STBPE_DERR_TIMEOUT) return fail(e, STBPE_E_TIMEOUT, "a bounded device-side wait gave up (tile pipeline)");
+    if (err & STBPE_DERR_TIMEOUT) return fail(e, STBPE_E_TIMEOUT, "a bounded device-side wait gave up (tile pipeline or a peer's flag)");
     if (err & STBPE_DERR_KEY_MISSING) return fail(e, STBPE_E_STATE, "selected pair missing from the pair table");
     return STBPE_OK;
 }
@@ -1069,6 +1069,27 @@ STBPE_VISIBLE int stbpe_mg_peer_open(stbpe_engine *e, const void *handles, int32
         CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
         e->mail_mapped[r] = p;
         e->d.mail[r] = (unsigned char *)p;
+    }
+    e->peers_open = true;
+    return STBPE_OK;
+}
+
+// The same set-up for ranks that live in one process (one GPU each, peer access between the devices
+// enabled by the caller): the mailboxes are handed over as plain device pointers.
+STBPE_VISIBLE int stbpe_mg_peer_mailbox(stbpe_engine *e, void **out) {
+    if (!e || !out) return STBPE_E_BADARG;
+    if (!e->mail_own) return fail(e, STBPE_E_STATE, "call stbpe_mg_peer_export first");
+    *out = e->mail_own;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_peer_set(stbpe_engine *e, const void *const *mailboxes, int32_t n) {
+    if (!e || !mailboxes) return STBPE_E_BADARG;
+    if (!e->mail_own) return fail(e, STBPE_E_STATE, "call stbpe_mg_peer_export first");
+    if (n != e->cfg.world_size) return fail(e, STBPE_E_BADARG, "one mailbox per rank is needed");
+    for (int r = 0; r < n; ++r) {
+        if (r != e->cfg.rank && !mailboxes[r]) return fail(e, STBPE_E_BADARG, "null mailbox");
+        e->d.mail[r] = r == e->cfg.rank ? e->mail_own : (unsigned char *)mailboxes[r];
     }
     e->peers_open = true;
     return STBPE_OK;

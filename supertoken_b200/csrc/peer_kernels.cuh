@@ -167,7 +167,11 @@ __device__ __forceinline__ void commit_from_mailbox(const EngineDev &e, int targ
     own->round = round;
     st->target = target;
     st->round_incomplete = 0;
-    if (!ok || st->stopped) return;
+    if (!ok) {  // a peer never answered: idle every later kernel of this engine; the host reads the error bit
+        st->stopped = 1;
+        return;
+    }
+    if (st->stopped) return;
     u64 bk = STBPE_EMPTY;
     i64 bc = 0;
     bool incomplete = false;

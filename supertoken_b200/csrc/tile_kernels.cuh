@@ -378,6 +378,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
     if (st->stopped || st->exchange_only) return;
     const uint32_t a = (uint32_t)st->cur_a, b = (uint32_t)st->cur_b, nw = (uint32_t)st->cur_new;
     const int m = st->merges_done;  // number of this merge (>= 1)
+    if (m < 1) return;              // nothing has been selected yet
     const bool same = (a == b);
 
     TilePipe pipe;

@@ -141,7 +141,7 @@ class Engine:
         st = self.state()
         bits = st.device_error
         if bits & 32:
-            raise RuntimeError("a bounded device-side wait gave up (tile pipeline)")
+            raise RuntimeError("a bounded device-side wait gave up (tile pipeline or a peer's flag)")
         if bits & (1 | 2 | 4):
             raise CapacityError("pair workspace capacity exceeded (pair table / delta buffers full)")
         if bits & 16:

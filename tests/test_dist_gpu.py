@@ -82,6 +82,50 @@ def test_emulated_ranks_repack_between_commit_and_apply():
         w.e.close()
 
 
+def test_peer_wait_runs_out_when_the_other_rank_never_sends():
+    # failure detection of the peer-memory rounds: rank 0 runs one round while rank 1 (an engine of
+    # the same process that never launches anything) raises no flag.  The wait in rank 0's kernels
+    # gives up after its two-second limit, the kernels that follow return at once, the host reads
+    # the time-out status, and the CUDA context stays usable.
+    import ctypes
+    import time
+    lib = L.load()
+    data = np.frombuffer(b"abcabcabd" * 2000, dtype=np.uint8).copy()
+    engines = []
+    for r in range(2):
+        e = Engine(len(data), base_vocab=256, max_merges=4, table_slots=1 << 16, world_size=2, rank=r)
+        e.append_bytes(data, None)
+        engines.append(e)
+    boxes = (ctypes.c_void_p * 2)()
+    for r, e in enumerate(engines):
+        buf = (ctypes.c_ubyte * 64)()
+        e._check(lib.stbpe_mg_peer_export(e._h, 256, buf))
+        box = ctypes.c_void_p()
+        e._check(lib.stbpe_mg_peer_mailbox(e._h, ctypes.byref(box)))
+        boxes[r] = box.value
+    e0 = engines[0]
+    e0._check(lib.stbpe_mg_peer_set(e0._h, boxes, 2))
+    t = time.perf_counter()
+    e0._check(lib.stbpe_mg_peer_run(e0._h, 1, 2, e0._s))   # two rounds: the second must not wait again
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t
+    assert 1.5 < waited < 6.0
+    st = e0.state()
+    assert st.device_error & 32
+    with pytest.raises(RuntimeError, match="wait gave up"):
+        e0.count_error()
+    # the device still works: a fresh single-rank engine trains as usual
+    e = Engine(len(data), base_vocab=256, max_merges=3, table_slots=1 << 16)
+    e.append_bytes(data, None)
+    e.count_initial()
+    e.train(3)
+    om, _, _ = O.train_flat(data.astype(np.int32), np.array([0, len(data)], dtype=np.int64), 256, 3, 1)
+    assert e.merges()[0] == om
+    e.close()
+    for x in engines:
+        x.close()
+
+
 def _nccl_rank(rank, world, port, target, q, native=False):
     import datetime
     import torch.distributed as dist
