@@ -23,8 +23,10 @@ Python package whose source tree is not present on the benchmark machine).
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
+import struct
 import subprocess
 import sys
 import tempfile
@@ -108,6 +110,15 @@ class ClockSampler:
         return out
 
 
+def merges_sha256(merges, counts) -> str:
+    """SHA-256 over the ordered (a, b, count) triples of a merge list (little-endian int32, int32,
+    int64): equal hashes at every N mean every GPU count learned the same merges with the same counts."""
+    h = hashlib.sha256()
+    for (a, b), c in zip(merges, counts):
+        h.update(struct.pack("<iiq", int(a), int(b), int(c)))
+    return h.hexdigest()
+
+
 def rank_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
@@ -122,29 +133,48 @@ def cpu_sample(corpus_np: np.ndarray, offsets_np: np.ndarray, n_bytes: int):
 
 
 def time_oracle(ids: np.ndarray, off: np.ndarray, steps: int, warmup: int):
-    """Seconds for exactly `steps` merges of the oracle's recount loop (after `warmup` merges);
-    the stream is restarted from a fresh copy when a stop rule fires before `steps`."""
+    """Seconds for exactly `steps` merges of the oracle's recount loop, started from merge 0 of a fresh
+    copy of the stream after `warmup` untimed merges on another copy (the GPU arm does the same: it
+    warms up, reloads the corpus and times the first merges).  The stream is restarted when a stop rule
+    fires before `steps`.  Returns (seconds, threads, merges of the first timed pass, their counts).
+    The thread count is set here to the cores this process may use (torch.distributed.run exports
+    OMP_NUM_THREADS=1 to its children)."""
     from oracle import oracle as O
     O.lib()
+    cores = O.set_threads()
+    if warmup:
+        O.train_flat(ids.copy(), off.copy(), 256, warmup, 1, copy=False)
     done, total = 0, 0.0
-    first = True
+    first_merges, first_counts = None, None
     while done < steps:
         cur_ids, cur_off = ids.copy(), off.copy()
-        w = warmup if first else 0
-        first = False
-        if w:
-            m, _, reason = O.train_flat(cur_ids, cur_off, 256, w, 1, copy=False)
-            base = 256 + len(m)
-        else:
-            base = 256
-        want = steps - done
         t = time.perf_counter()
-        m, _, reason = O.train_flat(cur_ids, cur_off, base, want, 1, copy=False)
+        m, c, reason = O.train_flat(cur_ids, cur_off, 256, steps - done, 1, copy=False)
         total += time.perf_counter() - t
         if not m:
             raise RuntimeError("oracle sample too small to learn a merge")
+        if first_merges is None:
+            first_merges, first_counts = list(m), list(c)
         done += len(m)
-    return total, O.num_threads()
+    return total, cores, first_merges, first_counts
+
+
+def make_corpus(gen: str, n_bytes: int, seed: int):
+    """The workload's bytes and row offsets as numpy arrays (generated on a GPU when there is one:
+    the generators give the same bytes on either backend, the GPU is just faster)."""
+    from supertoken_b200 import synth
+    try:
+        import torch
+        if torch.cuda.is_available():
+            c = getattr(synth, gen)(n_bytes=n_bytes, seed=seed, device="cuda:0")
+            data, off = c.data.cpu().numpy(), c.row_offsets.cpu().numpy()
+            del c
+            torch.cuda.empty_cache()
+            return data, off
+    except ImportError:
+        pass
+    c = getattr(synth, gen)(n_bytes=n_bytes, seed=seed)
+    return np.asarray(c.data), np.asarray(c.row_offsets)
 
 
 def run_reference_arm(args, wl):
@@ -157,6 +187,7 @@ def run_reference_arm(args, wl):
     gen, n_bytes, seed, merges, desc = wl
     if args.workload == "c3":
         from oracle import oracle as O
+        O.set_threads()
         n = min(1 << 25, n_bytes)
         ids, off = synth.config3_ids(n, seed=seed)
         ids, off = np.asarray(ids), np.asarray(off)
@@ -178,33 +209,41 @@ def run_reference_arm(args, wl):
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}), flush=True)
         return
-    # time per step such that the whole run ends within a few minutes
-    total_s = 150.0
-    per_step = total_s / max(args.steps + args.warmup, 1)
+    # The whole workload when W + K merges of it fit the time a bench run may take on this
+    # machine's cores; otherwise a prefix of the corpus, with the rate scaled to the full size.
+    budget_s = 150.0
     probe = getattr(synth, gen)(n_bytes=1 << 20, seed=seed)
     ids, off = cpu_sample(np.asarray(probe.data), np.asarray(probe.row_offsets), 1 << 20)
-    t, cores = time_oracle(ids, off, 3, 0)
-    # the recount costs about 2.5 ns per token on the first merges (a few thousand distinct pairs)
-    # and up to 20 ns per token late in a run (distinct pairs of the order of the tokens; measured
-    # with this oracle on 8 cores), so the sample is sized for the late regime
-    sec_per_token_merge = max(t / 3 / len(ids), 2.0e-8)
-    sample_bytes = int(min(max(per_step / sec_per_token_merge, 64 << 10), 256 << 20, n_bytes))
-    c = getattr(synth, gen)(n_bytes=sample_bytes, seed=seed)
-    ids, off = cpu_sample(np.asarray(c.data), np.asarray(c.row_offsets), sample_bytes)
-    t, cores = time_oracle(ids, off, args.steps, args.warmup)
-    scale = len(ids) / float(n_bytes)          # recount cost is linear in the corpus size
+    t, cores, _, _ = time_oracle(ids, off, 3, 0)
+    early = t / 3 / len(ids)                      # seconds per token and merge, first merges
+    n_steps = args.steps + args.warmup
+    whole = n_bytes <= (2 << 30) and n_steps <= 64 and 1.5 * early * n_bytes * n_steps <= budget_s
+    if whole:
+        data, off_all = make_corpus(gen, n_bytes, seed)
+        ids, off = data.astype(np.int32), off_all.astype(np.int64)
+        del data
+        sample = f"the whole corpus ({len(ids)} bytes), merges 0..{args.steps - 1} after {args.warmup} warm-up merges"
+    else:
+        # the recount costs up to 8x more per token late in a run (distinct pairs of the order of the
+        # tokens) than on the first merges, so a long run is sized for the late regime
+        rate = max(early, 2.0e-8) if n_steps > 64 else 1.5 * early
+        sample_bytes = int(min(max(budget_s / n_steps / rate, 64 << 10), 256 << 20, n_bytes))
+        c = getattr(synth, gen)(n_bytes=sample_bytes, seed=seed)
+        ids, off = cpu_sample(np.asarray(c.data), np.asarray(c.row_offsets), sample_bytes)
+        sample = (f"first {len(ids)} bytes of the corpus, {args.steps} merges; rate scaled by "
+                  f"{len(ids) / float(n_bytes):.5f} to the full corpus (a recount is linear in tokens)")
+    t, cores, m, c = time_oracle(ids, off, args.steps, args.warmup)
+    scale = len(ids) / float(n_bytes)
     value = args.steps / t * scale
     line = {
         "impl": "reference", "metric": "bpe_merges_per_sec", "value": value, "unit": "merges/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1000.0 * t / args.steps / scale, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int32", "data": "synthetic",
-        "config": {"workload": desc, "name": args.workload, "merges_timed": args.steps},
-        "cpu_baseline": {"value": value, "unit": "merges/s", "cores": cores, "kind": "port",
-                         "sample": f"first {len(ids)} bytes of the corpus, {args.steps} merges; "
-                                   f"rate scaled by {scale:.5f} to the full corpus (a recount is linear in tokens; "
-                                   f"a small sample has more distinct pairs per token than the full corpus, which "
-                                   f"costs the recount up to 8x more per token than the first merges at full size)"},
+        "config": {"workload": desc, "name": args.workload, "merges_timed": args.steps,
+                   "same_workload": bool(whole), "measured_seconds": t,
+                   "merges_sha256": merges_sha256(m[:args.steps], c[:args.steps]) if whole else None},
+        "cpu_baseline": {"value": value, "unit": "merges/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "merges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -374,6 +413,8 @@ def main():
     eng.count_initial()
     sel_ms, mrg_ms, ref_ms, repack_ms = eng.train_timed(K)
     torch.cuda.synchronize()
+    st_t = eng.state()
+    tile_bytes = float(st_t.tile_bytes_in + st_t.tile_bytes_out)   # what the merge kernel's bulk copies moved
     merges_again, _, _ = eng.merges(0, eng.state().merges_done)
     assert merges_again == merges_gpu, "merge list changed between two runs on the same input"
     algo_bytes = 4.0 * float(live_before.sum())
@@ -398,18 +439,31 @@ def main():
     e2e = len(learned) / e2e_s
 
     cpu = None
+    oracle_ok, oracle_n = None, 0
     if not args.no_cpu_baseline:
-        sample_bytes = min(64 << 20, n_bytes)
-        ids, off = cpu_sample(host.numpy(), off_np, sample_bytes)
-        n_cpu = 12
-        t_cpu, cores = time_oracle(ids, off, n_cpu, 0)
-        if t_cpu < 8.0:  # aim at about 12 s of CPU work on this machine's cores
-            n_cpu = int(min(max(12.0 / (t_cpu / 12), 12), 600))
-            t_cpu, cores = time_oracle(ids, off, n_cpu, 0)
-        scale = len(ids) / float(n_tokens)
-        cpu = {"value": n_cpu / t_cpu * scale, "unit": "merges/s", "cores": cores, "kind": "port",
-               "sample": f"first {len(ids)} bytes, first {n_cpu} merges, {t_cpu:.1f} s; rate scaled by "
-                         f"{scale:.4f} to the full corpus (recount cost is linear in tokens)"}
+        # The oracle on this machine's cores: the first merges of the WHOLE corpus when a few of them
+        # fit about 25 s (then the same run also checks the GPU's merges and counts against the oracle),
+        # else a prefix of the corpus with the rate scaled by its share of the tokens.
+        ids, off = cpu_sample(host.numpy(), off_np, min(32 << 20, n_bytes))
+        t_probe, cores, _, _ = time_oracle(ids, off, 3, 0)
+        per_merge_full = t_probe / 3 / len(ids) * n_tokens * 1.3
+        if n_tokens <= (2 << 30) and 2 * per_merge_full <= 60.0:
+            n_cpu = int(min(max(25.0 / per_merge_full, 2), 8, len(learned)))
+            ids, off = host.numpy().astype(np.int32), off_np.astype(np.int64)
+            t_cpu, cores, om, oc = time_oracle(ids, off, n_cpu, 0)
+            oracle_n = min(len(om), len(merges_gpu))
+            oracle_ok = bool(om[:oracle_n] == merges_gpu[:oracle_n] and
+                             list(oc[:oracle_n]) == [int(x) for x in counts_gpu[:oracle_n]])
+            cpu = {"value": n_cpu / t_cpu, "unit": "merges/s", "cores": cores, "kind": "port",
+                   "sample": f"the whole corpus ({n_tokens} bytes), merges 0..{n_cpu - 1}, {t_cpu:.1f} s, not scaled"}
+        else:
+            n_cpu = 12
+            t_cpu, cores, _, _ = time_oracle(ids, off, n_cpu, 0)
+            scale = len(ids) / float(n_tokens)
+            cpu = {"value": n_cpu / t_cpu * scale, "unit": "merges/s", "cores": cores, "kind": "port",
+                   "sample": f"first {len(ids)} bytes, first {n_cpu} merges, {t_cpu:.1f} s; rate scaled by "
+                             f"{scale:.4f} to the full corpus (recount cost is linear in tokens)"}
+        del ids, off
 
     line = {
         "metric": "bpe_merges_per_sec", "value": value, "unit": "merges/s", "n_gpus": 1, "steps": done,
@@ -417,6 +471,8 @@ def main():
         "vs_baseline": None, "dtype": "int32", "data": "synthetic",
         "config": {"workload": desc, "name": args.workload, "corpus_bytes": n_tokens, "rows": len(off_np) - 1,
                    "merges_timed": done, "first_merge": 0, "stop_reason": int(st.stop_reason),
+                   "merges_sha256": merges_sha256(merges_gpu, counts_gpu),
+                   "oracle_prefix_ok": oracle_ok, "oracle_prefix_merges": oracle_n,
                    "l2": "inputs larger than L2 (4 bytes x tokens per merge)", "tile_tokens": 1024},
         "pair_count": {"kernel": "count_dense_kernel (byte-level path)", "call_ms": count_call_ms, "ms": count_ms, "gbs": 4.0 * n_tokens / (count_ms / 1e3) / 1e9,
                        "frac_of_measured_peak": 4.0 * n_tokens / (count_ms / 1e3) / 1e9 / peak,
@@ -426,10 +482,10 @@ def main():
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "algorithmic_bytes": algo_bytes, "kernel_ms": mrg_ms, "launches": done,
                      "other_kernels_ms": {"select_kernel": sel_ms, "refresh_kernel": ref_ms, "repack": repack_ms},
-                     "traffic": 0.711 * algo_bytes / done,
-                     "traffic_note": "DRAM read+write per launch = 0.711 x algorithmic bytes: ncu over merges 1-1500 of a "
-                                     "64 MiB slice (115.7 GB of traffic for 162.7 GB algorithmic), scaled by live tokens; "
-                                     "later merges visit fewer tiles, so the factor of the full job is lower"},
+                     "traffic": tile_bytes / done,
+                     "traffic_note": "bytes per launch that the kernel's own bulk copies moved in this run (tiles and tile "
+                                     "records read + rewritten tile parts and records stored, counted by the kernel); "
+                                     "the ncu summaries under profiles/ give dram__bytes for the same kernel"},
         "e2e": {"value": e2e, "unit": "merges/s", "seconds": e2e_s,
                 "h2d_bytes_per_step": (n_tokens + off_np.nbytes) / max(len(learned), 1),
                 "d2h_bytes_per_step": 24.0},

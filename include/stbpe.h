@@ -63,6 +63,8 @@ typedef struct stbpe_state {
     double count_kernel_ms;   /* device time of the histogram kernel(s) of the last count */
     double count_convert_ms;  /* 16-bit-vocabulary path only: device time of moving the directly
                                  indexed counters into the pair table (0 otherwise) */
+    int64_t tile_bytes_in;    /* merge kernel, since the last load: bytes of tiles and tile records read ... */
+    int64_t tile_bytes_out;   /* ... and bytes of rewritten tile parts and records stored (statistics) */
 } stbpe_state;
 
 /* Lifetime.  Replaces GPUBPETrainer's per-fit device contexts and workspaces
@@ -77,6 +79,8 @@ const char *stbpe_version(void);
  * (gpu_tokenizer/cpu_packer.py:17-61, datasets.py:75-84, bpe_trainer.py:137-222).
  * Rows are appended after the rows of earlier calls; empty rows own no pair and
  * vanish.  row_offsets has n_rows+1 entries (host memory), offsets into data.
+ * Appending is possible until the first merge has been applied: afterwards the tiles of the
+ * stream are no longer dense and the call returns STBPE_E_STATE (call stbpe_reset first).
  * stbpe_reset drops the stream, the table and the merge log. */
 int stbpe_reset(stbpe_engine *e);
 int stbpe_append_bytes(stbpe_engine *e, const uint8_t *data /* host or device */, int64_t n,
@@ -237,7 +241,8 @@ int stbpe_rows_apply_merge(int32_t *tokens, uint8_t *valid, int32_t *lengths, in
  *   - B*(L-1) must not exceed 65 536 pair positions; larger batches get STBPE_E_CAPACITY and a
  *     message in err (err may be NULL).  Nothing is computed in that case.
  *   - The first call on each device looks up the block's device address
- *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *     (cudaGetSymbolAddress).  Every call reads the number of unique pairs back to the host and
+ *     synchronises the stream, so make no call while the stream is being captured.
  *   - All calls share the block, which keeps the previous call's contents; it is cleared at the
  *     start of each call.  Calls that overlap on the GPU race: serialise them. */
 int stbpe_rows_count_pairs_noalloc(const int32_t *tokens, const uint8_t *valid, int64_t B, int64_t L,

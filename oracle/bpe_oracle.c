@@ -362,6 +362,16 @@ ORC_EXPORT int64_t orc_train_flat(int32_t *ids, int64_t *off, int64_t n_rows, in
     return done;
 }
 
+/* Number of threads of the threaded recount (launchers such as torch.distributed.run export
+ * OMP_NUM_THREADS=1 to their children, which would otherwise time a single-threaded baseline). */
+ORC_EXPORT void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_EXPORT int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

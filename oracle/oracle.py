@@ -51,6 +51,8 @@ def lib() -> ctypes.CDLL:
         L.orc_train_flat.restype = i64
         L.orc_train_flat.argtypes = [vp, vp, i64, i32, i64, ctypes.c_int, vp, vp, vp]
         L.orc_num_threads.restype = ctypes.c_int
+        L.orc_set_threads.restype = None
+        L.orc_set_threads.argtypes = [ctypes.c_int]
         _lib = L
     return _lib
 
@@ -61,6 +63,17 @@ def _p(a: np.ndarray) -> ctypes.c_void_p:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_threads(n: Optional[int] = None) -> int:
+    """Threads of the threaded recount; default = the cores this process may run on."""
+    if n is None:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+    lib().orc_set_threads(int(n))
+    return num_threads()
 
 
 # --------------------------------------------------------------------------- rows API

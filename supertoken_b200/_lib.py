@@ -27,7 +27,8 @@ class State(ctypes.Structure):
                 ("live_tokens", ctypes.c_int64), ("table_keys", ctypes.c_int64),
                 ("table_slots", ctypes.c_int64), ("device_error", ctypes.c_uint32),
                 ("n_tiles", ctypes.c_int32), ("fixups", ctypes.c_int64), ("repacks", ctypes.c_int64), ("work_tiles", ctypes.c_int64), ("count_kernel_ms", ctypes.c_double),
-                ("count_convert_ms", ctypes.c_double)]
+                ("count_convert_ms", ctypes.c_double),
+                ("tile_bytes_in", ctypes.c_int64), ("tile_bytes_out", ctypes.c_int64)]
 
 
 # every symbol include/stbpe.h declares: name -> (restype, argtypes)

@@ -28,7 +28,7 @@ import torch
 from . import _lib as L
 from .base import BaseTrainer
 from .engine import Engine
-from .export import bytes_to_unicode, write_artifacts
+from .export import GPUBPETokenizer, build_artifacts, bytes_to_unicode, write_artifacts
 
 logger = logging.getLogger(__name__)
 UINT32_MAX = (1 << 32) - 1
@@ -219,12 +219,15 @@ class GPUBPETrainer(BaseTrainer):
                 "requested_top_k": int(top_k), "order": 2, "histogram_size": int(keys.numel()), "source": "ngram"}
 
     # ------------------------------------------------------------------ the loop
-    def _make_engine(self, n_tokens: int) -> Engine:
+    def _make_engine(self, n_tokens: int, first_new_id: Optional[int] = None) -> Engine:
+        """``first_new_id``: id the engine gives its first merge (a stream restored from a checkpoint
+        already holds the ids of the merges made before it was written)."""
         dev = torch.device(self.device)
         if self._engine is not None:
             self._engine.close()
-        self._engine = Engine(max(int(n_tokens), 1), base_vocab=self.base_vocab,
-                              max_merges=max(self.target_merges, 1), device=dev,
+        base = self.base_vocab if first_new_id is None else int(first_new_id)
+        self._engine = Engine(max(int(n_tokens), 1), base_vocab=base,
+                              max_merges=max(self.target_merges - (base - self.base_vocab), 1), device=dev,
                               table_slots=self.table_slots)
         return self._engine
 
@@ -238,11 +241,14 @@ class GPUBPETrainer(BaseTrainer):
         CUDA tensors, as the reference's batchers yield them (``gpu_tokenizer/datasets.py:88-92``)."""
         if checkpoint_interval is not None and checkpoint_dir is None:
             raise ValueError("checkpoint_interval requires checkpoint_dir")
+        restored_rows = None
         if resume_state is not None:
-            # resume (bpe_trainer.py:2938-2986): the merges of the checkpoint are replayed on the
-            # batches without counting, then the loop continues; merges are a pure function of the
-            # corpus, so the result equals an uninterrupted run
-            self.load_state_dict(resume_state)
+            # resume (bpe_trainer.py:2938-2986).  A checkpoint that holds the rewritten rows continues
+            # from them; otherwise its merges are replayed on the batches without counting.  Merges
+            # are a pure function of the corpus (and of the restored tie-break generator), so either
+            # way the result equals an uninterrupted run.
+            record = self.load_state_dict(resume_state)
+            restored_rows = record.get("sequences")
             warm_start_merges = list(self.merges)
         elif warm_start_merges is None and warm_start_plan is not None:
             warm_start_merges = [tuple(p) for p in warm_start_plan.get("merges", [])]
@@ -250,9 +256,22 @@ class GPUBPETrainer(BaseTrainer):
             batches = list(batches)
             plan = self.precompute_warm_start_plan(batches, int(warm_start_ngrams), device=warm_start_device or self.device)
             warm_start_merges = plan["merges"]
+        t0 = time.perf_counter()
+        if restored_rows is not None:
+            if self._sharded_mode() is not None:
+                self._reject_in_sharded_mode(warm_start_merges, checkpoint_interval)
+            lens = np.fromiter((len(r) for r in restored_rows), dtype=np.int64, count=len(restored_rows))
+            off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+            ids = np.fromiter((t for r in restored_rows for t in r), dtype=np.int32, count=int(off[-1]))
+            eng = self._make_engine(len(ids), first_new_id=self.base_vocab + len(self.merges))
+            if len(ids):
+                eng.append_ids(ids, off)
+                self.bytes_h2d += ids.nbytes
+                self.h2d_events += 1
+            return self._run_loop(eng, log_every, t0, None, checkpoint_interval, checkpoint_dir,
+                                  already=list(self.merges), dataset_state=dataset_state)
         flat: List[Tuple[torch.Tensor, np.ndarray]] = [_flatten_batch(b) for b in batches]
         total = sum(int(ids.numel()) for ids, _ in flat)
-        t0 = time.perf_counter()
         mode = self._sharded_mode()
         if mode is not None:
             self._reject_in_sharded_mode(warm_start_merges, checkpoint_interval)
@@ -264,18 +283,31 @@ class GPUBPETrainer(BaseTrainer):
                 if not ids.is_cuda:
                     self.bytes_h2d += ids.numel() * 4
                     self.h2d_events += 1
-        return self._run_loop(eng, log_every, t0, warm_start_merges, checkpoint_interval, checkpoint_dir)
+        return self._run_loop(eng, log_every, t0, warm_start_merges, checkpoint_interval, checkpoint_dir,
+                              dataset_state=dataset_state)
 
-    def fit_bytes(self, data, row_offsets=None, log_every: int = 0) -> dict:
+    def fit_bytes(self, data, row_offsets=None, log_every: int = 0, *, warm_start_merges=None,
+                  checkpoint_interval: Optional[int] = None, checkpoint_dir: Optional[str] = None,
+                  resume_state=None, dataset_state=None) -> dict:
         """Fast ingest: one uint8 buffer (host or device) plus row offsets; rows are what
         the reference calls files / documents.  Not part of the reference API: padded
-        ``[B, L]`` int32 batches cost five host bytes per input byte."""
+        ``[B, L]`` int32 batches cost five host bytes per input byte.  Warm start, checkpoint
+        interval and resume behave as in ``fit``."""
+        if checkpoint_interval is not None and checkpoint_dir is None:
+            raise ValueError("checkpoint_interval requires checkpoint_dir")
         if isinstance(data, np.ndarray):
             data = torch.from_numpy(np.ascontiguousarray(data, dtype=np.uint8))
+        if resume_state is not None:
+            record = self.load_state_dict(resume_state)
+            if record.get("sequences") is not None:
+                return self.fit([], log_every=log_every, checkpoint_interval=checkpoint_interval,
+                                checkpoint_dir=checkpoint_dir, resume_state=resume_state,
+                                dataset_state=dataset_state)
+            warm_start_merges = list(self.merges)
         t0 = time.perf_counter()
         mode = self._sharded_mode()
         if mode is not None:
-            self._reject_in_sharded_mode(None, None)
+            self._reject_in_sharded_mode(warm_start_merges, checkpoint_interval)
             off = Engine._offsets(row_offsets, int(data.numel()))
             return self._fit_sharded(mode, [(data, off)], True, log_every, t0)
         eng = self._make_engine(data.numel())
@@ -283,16 +315,24 @@ class GPUBPETrainer(BaseTrainer):
         if not data.is_cuda:
             self.bytes_h2d += data.numel()
             self.h2d_events += 1
-        return self._run_loop(eng, log_every, t0, None, None, None)
+        return self._run_loop(eng, log_every, t0, warm_start_merges, checkpoint_interval, checkpoint_dir,
+                              dataset_state=dataset_state)
 
     def _run_loop(self, eng: Engine, log_every: int, t0: float, warm_start_merges,
-                  checkpoint_interval, checkpoint_dir) -> dict:
+                  checkpoint_interval, checkpoint_dir, already: Optional[List[Tuple[int, int]]] = None,
+                  dataset_state=None) -> dict:
+        """``already``: merges that the loaded stream holds already (resume from the rows of a
+        checkpoint); the engine numbers its own merges after them."""
         timings = {k: StageTiming(k) for k in ("pair_count", "apply_merge", "host_sync")}
         events: List[dict] = []
-        self.merges = []
+        self.merges = list(already) if already else []
         self.merge_counts = []
-        self.vocab_size = self.base_vocab
-        warm = list(warm_start_merges) if warm_start_merges is not None else list(self._seed_warm_start_merges)
+        self.vocab_size = self.base_vocab + len(self.merges)
+        skip = len(self.merges)   # merges the engine's own log does not hold
+        if already:
+            warm: List[Tuple[int, int]] = []
+        else:
+            warm = list(warm_start_merges) if warm_start_merges is not None else list(self._seed_warm_start_merges)
 
         t = time.perf_counter()
         eng.count_initial()
@@ -311,35 +351,42 @@ class GPUBPETrainer(BaseTrainer):
             self.vocab_size += 1
             warm_applied += 1
 
+        def checkpoint():
+            self.save_checkpoint(checkpoint_dir, dataset_state=dataset_state)
+
         t = time.perf_counter()
         remaining = self.target_merges - len(self.merges)
         reason = L.RUNNING
         if remaining > 0:
             if self.randomize_ties:
-                reason = self._loop_random_ties(eng, remaining)
+                reason = self._loop_random_ties(eng, remaining, checkpoint_interval,
+                                                checkpoint if checkpoint_dir else None)
             else:
                 step = checkpoint_interval if checkpoint_interval else remaining
                 while remaining > 0 and reason in (L.RUNNING, L.STOP_TARGET):
                     n = min(step, remaining)
                     eng.train(n)
+                    th = time.perf_counter()
                     st = eng.state()
-                    got, counts, _ = eng.merges(len(self.merges), st.merges_done - len(self.merges))
+                    have = len(self.merges) - skip
+                    got, counts, _ = eng.merges(have, st.merges_done - have)
+                    timings["host_sync"].record(time.perf_counter() - th)   # merge log back to the host
+                    self.bytes_d2h += len(got) * 24
+                    self.d2h_events += 1
                     self.merges.extend(got)
                     self.merge_counts.extend(int(c) for c in counts)
                     self.vocab_size = self.base_vocab + len(self.merges)
                     remaining = self.target_merges - len(self.merges)
                     reason = st.stop_reason
                     if checkpoint_interval and checkpoint_dir and remaining > 0:
-                        self.save_checkpoint(checkpoint_dir)
+                        checkpoint()
                     if len(got) < n:
                         break
         loop_s = time.perf_counter() - t
-        return self._finalize(eng.state(), reason, timings, events, warm_applied, loop_s, t0, log_every)
+        return self._finalize(eng.state(), reason, timings, events, warm_applied + skip, loop_s, t0, log_every)
 
     def _finalize(self, st, reason, timings, events, warm_applied, loop_s, t0, log_every) -> dict:
         timings["apply_merge"].record(loop_s)
-        self.bytes_d2h += len(self.merges) * 16
-        self.d2h_events += 1
         if log_every and log_every > 0:
             for step, ((a, b), c) in enumerate(zip(self.merges[warm_applied:], self.merge_counts)):
                 if step % log_every == 0:
@@ -356,7 +403,10 @@ class GPUBPETrainer(BaseTrainer):
         self._last_stats = {"live_tokens": int(st.live_tokens), "table_keys": int(st.table_keys),
                             "table_slots": int(st.table_slots), "loop_s": loop_s,
                             "total_s": time.perf_counter() - t0, "stop_reason": int(reason)}
-        merge_log = [{"merge": i, "bytes_d2h": 16} for i in range(len(self.merge_counts))]
+        # The loop runs on the device: nothing is copied to the host per merge, the merge log comes
+        # back once per train call (24 bytes per merge: pair, count, live tokens), so there is no
+        # per-merge transfer record to report.
+        n_learned = len(self.merge_counts)
         return {
             "base_vocab": self.base_vocab,
             "vocab_size": self.vocab_size,
@@ -365,10 +415,11 @@ class GPUBPETrainer(BaseTrainer):
             "transfer_metrics": {
                 "bytes_h2d": self.bytes_h2d, "bytes_d2h": self.bytes_d2h,
                 "h2d_events": self.h2d_events, "d2h_events": self.d2h_events,
-                "merge_stats": merge_log, "sync_intervals": [],
+                "merge_stats": [], "sync_intervals": [],
                 "per_device": {self.device: {"bytes_h2d": self.bytes_h2d, "bytes_d2h": self.bytes_d2h}},
-                "per_stage": {k: {"h2d": 0, "d2h": 0} for k in ("pair_count", "apply_merge", "host_sync")},
-                "avg_d2h_bytes_per_merge": (self.bytes_d2h / len(merge_log)) if merge_log else 0.0,
+                "per_stage": {"pair_count": {"h2d": self.bytes_h2d, "d2h": 0}, "apply_merge": {"h2d": 0, "d2h": 0},
+                              "host_sync": {"h2d": 0, "d2h": self.bytes_d2h}},
+                "avg_d2h_bytes_per_merge": (self.bytes_d2h / n_learned) if n_learned else 0.0,
                 "cpu_fallback": {"batches": 0, "ratio": 0.0},
             },
             "telemetry": {
@@ -470,10 +521,12 @@ class GPUBPETrainer(BaseTrainer):
         return self._finalize(st, reason, timings, events, 0, loop_s, t0, log_every)
 
 
-    def _loop_random_ties(self, eng: Engine, remaining: int) -> int:
+    def _loop_random_ties(self, eng: Engine, remaining: int, checkpoint_interval=None, checkpoint=None) -> int:
         """Host-driven loop for ``randomize_ties``: the seeded ``random.Random`` picks an index
         into the tied candidates in ascending key order (``bpe_trainer.py:915-923``,
-        ``trainers/bpe_gpu.py:112-123``)."""
+        ``trainers/bpe_gpu.py:112-123``).  ``checkpoint`` is called every ``checkpoint_interval``
+        merges (the checkpoint carries the generator's state, so a resumed run draws on)."""
+        since = 0
         while remaining > 0:
             key, count, ties = eng.select_best(with_ties=True)
             if key is None:
@@ -489,6 +542,10 @@ class GPUBPETrainer(BaseTrainer):
             self.merge_counts.append(count)
             self.vocab_size += 1
             remaining -= 1
+            since += 1
+            if checkpoint is not None and checkpoint_interval and since >= checkpoint_interval and remaining > 0:
+                checkpoint()
+                since = 0
         return L.STOP_TARGET
 
     # ------------------------------------------------------------------ state / artifacts
@@ -509,35 +566,228 @@ class GPUBPETrainer(BaseTrainer):
             s["salt_configured"] = True
         return s
 
-    def state_dict(self, *args, **kwargs) -> dict:
-        return {"schema_version": CHECKPOINT_SCHEMA_VERSION,
-                "trainer": {"base_vocab": self.base_vocab, "vocab_size": self.vocab_size,
-                            "target_merges": self.target_merges, "merges": [list(p) for p in self.merges],
-                            "merge_step": len(self.merges), "privacy": self._privacy_summary()},
-                "autoscaler": {}, "dataset": {}, "rng": {}}
+    # Checkpoints follow the reference's layout (``gpu_tokenizer/bpe_trainer.py:1450-1601``,
+    # ``:1890-1948``; ``gpu_tokenizer/trainers/base.py:17-41``): ``state_dict`` returns
+    # ``{"payload": <schema v1: version / trainer / autoscaler / dataset / rng>, "tensors": {...}}``,
+    # ``save_checkpoint`` writes the payload as ``state.json`` and the tensors as ``tensors.pt``.
+    # The tensors are the pair histogram (ascending keys, int64 counts), which the reference keeps as
+    # its cached histogram; ``dataset.batches.sequences`` are the rewritten rows, from which a
+    # resumed ``fit`` continues without replaying the merges.
+    SEQUENCE_DUMP_LIMIT = 1 << 24  # rows are written as Python int lists, as the reference does
 
-    def load_state_dict(self, state_dict: Mapping[str, Any], *args, **kwargs) -> dict:
-        tr = dict(state_dict.get("trainer", {}))
-        self.base_vocab = int(tr.get("base_vocab", self.base_vocab))
-        self.merges = [tuple(map(int, p)) for p in tr.get("merges", [])]
-        self.vocab_size = int(tr.get("vocab_size", self.base_vocab + len(self.merges)))
-        self.target_merges = int(tr.get("target_merges", self.target_merges))
+    @staticmethod
+    def _encode_random_state(state):
+        if isinstance(state, (tuple, list)):
+            return [GPUBPETrainer._encode_random_state(x) for x in state]
+        return state
+
+    @staticmethod
+    def _decode_random_state(state):
+        if isinstance(state, (tuple, list)):
+            return tuple(GPUBPETrainer._decode_random_state(x) for x in state)
+        return state
+
+    def _current_rows(self) -> Optional[List[List[int]]]:
+        """Rows of the engine's stream as it stands (after the merges applied so far)."""
+        eng = self._engine
+        if eng is None or not getattr(eng, "_h", None) or not eng._h.value:
+            return None
+        st = eng.state()
+        if st.live_tokens > self.SEQUENCE_DUMP_LIMIT:
+            return None
+        ids, off = eng.export_stream()
+        return [ids[int(off[i]):int(off[i + 1])].tolist() for i in range(len(off) - 1)]
+
+    def state_dict(self, *, current_batches=None, include_batches: bool = True, stage_timings=None,
+                   stage_event_log=None, host_sync_events=None, device_snapshot_log=None,
+                   dataset_state=None) -> dict:
+        model = {"base_vocab": int(self.base_vocab), "target_merges": int(self.target_merges),
+                 "vocab_size": int(self.vocab_size), "merges": [list(map(int, p)) for p in self.merges],
+                 "merge_step": len(self.merges), "privacy_mode": bool(self.privacy_mode),
+                 "randomize_ties": bool(self.randomize_ties),
+                 "tie_seed": int(self.tie_seed) if self.tie_seed is not None else None,
+                 "tie_seed_effective": int(self._tie_seed_value)}
+        if self._privacy_hash_salt:
+            model["privacy_salt"] = self._privacy_hash_salt.hex()
+        logs: dict = {"merge_transfer_log": [], "sync_intervals": [], "transfer_stage_totals": {}}
+        progress = {}
+        if stage_timings is not None:
+            progress["stage_timings"] = {k: list(v.samples) for k, v in stage_timings.items()}
+        for name, val in (("stage_event_log", stage_event_log), ("host_sync_events", host_sync_events),
+                          ("device_snapshot_log", device_snapshot_log)):
+            if val is not None:
+                progress[name] = [dict(x) for x in val]
+        if progress:
+            logs["telemetry_progress"] = progress
+        trainer = {
+            "model": model,
+            "warm_start": {"plan": None, "applied": bool(self._seed_warm_start_merges),
+                           "freeze": bool(self.freeze_warm_start),
+                           "seed_merges": [list(map(int, p)) for p in self._seed_warm_start_merges],
+                           "frozen_pair_keys": []},
+            "histogram_cache": {"enable": False, "valid": False, "force_recount": False,
+                                "sizes": {"keys": 0, "counts": 0}},
+            "counters": {"bytes_h2d": int(self.bytes_h2d), "bytes_d2h": int(self.bytes_d2h),
+                         "h2d_events": int(self.h2d_events), "d2h_events": int(self.d2h_events)},
+            "logs": logs,
+            "privacy": self._privacy_summary(),
+        }
+        dataset: dict = {"cpu_fallback_batches": 0, "last_cpu_fallback_ratio": 0.0}
+        if self._active_batch_size is not None:
+            dataset["active_batch_size"] = int(self._active_batch_size)
+        if include_batches:
+            rows = None
+            if current_batches is not None:
+                rows = []
+                for b in current_batches:
+                    ids, off = _flatten_batch(b)
+                    flat = ids.cpu().numpy()
+                    rows.extend(flat[int(off[i]):int(off[i + 1])].tolist() for i in range(len(off) - 1))
+            else:
+                rows = self._current_rows()
+            if rows is not None:
+                dataset["batches"] = {"sequences": rows, "has_gpu": True,
+                                      "active_batch_size": self._active_batch_size}
+        if isinstance(dataset_state, Mapping):
+            offsets = dataset_state.get("stream_offsets")
+            if isinstance(offsets, Mapping) and offsets:
+                dataset["stream_offsets"] = {str(k): int(v) for k, v in offsets.items() if isinstance(k, str)}
+            try:
+                bs = int(dataset_state.get("batch_size")) if dataset_state.get("batch_size") is not None else None
+            except (TypeError, ValueError):
+                bs = None
+            if bs and bs > 0:
+                dataset["stream_batch_size"] = bs
+        rng: dict = {}
+        if self.randomize_ties and self._tie_rng is not None:
+            rng["tie_breaker"] = {"seed": int(self._tie_seed_value),
+                                  "state": self._encode_random_state(self._tie_rng.getstate())}
+        auto_state = self.autoscaler.state_dict() if hasattr(self.autoscaler, "state_dict") else {}
+        payload = {"version": CHECKPOINT_SCHEMA_VERSION, "trainer": trainer,
+                   "autoscaler": {"state": auto_state}, "dataset": dataset}
+        if rng:
+            payload["rng"] = rng
+        tensors = {"cached_pair_keys": torch.empty((0,), dtype=torch.long),
+                   "cached_pair_counts": torch.empty((0,), dtype=torch.int64)}
+        eng = self._engine
+        if eng is not None and getattr(eng, "_h", None) and eng._h.value:
+            st = eng.state()
+            if 0 < st.table_keys <= self.SEQUENCE_DUMP_LIMIT:
+                keys, counts = eng.export_histogram()
+                tensors = {"cached_pair_keys": keys.cpu(), "cached_pair_counts": counts.cpu()}
+                trainer["histogram_cache"]["sizes"] = {"keys": int(keys.numel()), "counts": int(counts.numel())}
+        return {"payload": payload, "tensors": tensors}
+
+    def load_state_dict(self, state_dict: Mapping[str, Any], *, device_contexts=None, use_cuda: bool = False) -> dict:
+        """Restore merges, privacy settings and the tie-break generator (``bpe_trainer.py:1603-1888``).
+        Accepts the reference layout (``payload`` / ``tensors``), a bare payload, and this package's
+        earlier flat layout.  Returns the resume record ``fit`` works from."""
+        empty = {"current_batches": None, "gpu_batches": None, "scale_state": None, "step": len(self.merges),
+                 "stage_timings": None, "stage_event_log": [], "host_sync_events": [],
+                 "device_snapshot_log": [], "dataset_state": None, "sequences": None}
+        if not state_dict:
+            return empty
+        payload = state_dict.get("payload", state_dict)
+        trainer = dict(payload.get("trainer", {}) or {})
+        model = trainer.get("model") if isinstance(trainer.get("model"), Mapping) else trainer
+        self.base_vocab = int(model.get("base_vocab", self.base_vocab))
+        self.target_merges = int(model.get("target_merges", self.target_merges))
+        self.merges = [tuple(map(int, p)) for p in model.get("merges", [])]
+        self.merge_counts = []
+        self.vocab_size = int(model.get("vocab_size", self.base_vocab + len(self.merges)))
+        if model.get("privacy_mode") is not None:
+            self.privacy_mode = bool(model["privacy_mode"])
+        if model.get("randomize_ties") is not None:
+            self.randomize_ties = bool(model["randomize_ties"])
+        elif model.get("privacy_mode") is not None:
+            self.randomize_ties = self.privacy_mode
+        if "tie_seed" in model:
+            self.tie_seed = int(model["tie_seed"]) if model["tie_seed"] is not None else None
+        if model.get("tie_seed_effective") is not None:
+            self._tie_seed_value = int(model["tie_seed_effective"])
+        elif self.tie_seed is not None:
+            self._tie_seed_value = int(self.tie_seed)
+        if model.get("privacy_salt") is not None:
+            try:
+                self._privacy_hash_salt = bytes.fromhex(str(model["privacy_salt"]))
+            except ValueError:
+                self._privacy_hash_salt = str(model["privacy_salt"]).encode("utf-8")
+        privacy = trainer.get("privacy")
+        if isinstance(privacy, Mapping):
+            mode = str(privacy.get("mode", "")).lower()
+            if mode == "none":
+                self.privacy_mode = False
+            elif mode in ("hash-merges", "tie-randomize"):
+                self.privacy_mode = True
+            if privacy.get("randomize_ties") is not None:
+                self.randomize_ties = bool(privacy["randomize_ties"])
+            if privacy.get("tie_seed_effective") is not None:
+                self._tie_seed_value = int(privacy["tie_seed_effective"])
+        warm = trainer.get("warm_start") if isinstance(trainer.get("warm_start"), Mapping) else {}
+        self.freeze_warm_start = bool(warm.get("freeze", self.freeze_warm_start))
         self._seed_warm_start_merges = list(self.merges)
+        rng_state = None
+        tie = (payload.get("rng") or {}).get("tie_breaker") if isinstance(payload.get("rng"), Mapping) else None
+        if isinstance(tie, Mapping):
+            if tie.get("seed") is not None:
+                self._tie_seed_value = int(tie["seed"])
+            if tie.get("state") is not None:
+                rng_state = self._decode_random_state(tie["state"])
         self._reset_tie_rng()
-        return dict(state_dict)
+        if rng_state is not None and self._tie_rng is not None:
+            self._tie_rng.setstate(rng_state)
+        dataset = payload.get("dataset") if isinstance(payload.get("dataset"), Mapping) else {}
+        if dataset.get("active_batch_size") is not None:
+            self._active_batch_size = int(dataset["active_batch_size"])
+        sequences = None
+        batches = dataset.get("batches")
+        if isinstance(batches, Mapping) and isinstance(batches.get("sequences"), list):
+            sequences = [[int(t) for t in row] for row in batches["sequences"]]
+        stream_state = {k: dataset[k] for k in ("stream_offsets", "stream_batch_size") if k in dataset} or None
+        progress = ((trainer.get("logs") or {}).get("telemetry_progress") or {}) if isinstance(trainer.get("logs"), Mapping) else {}
+        out = dict(empty)
+        out.update({"step": int(model.get("merge_step", len(self.merges))), "sequences": sequences,
+                    "dataset_state": stream_state, "stage_timings": progress.get("stage_timings"),
+                    "stage_event_log": list(progress.get("stage_event_log", [])),
+                    "host_sync_events": list(progress.get("host_sync_events", [])),
+                    "device_snapshot_log": list(progress.get("device_snapshot_log", []))})
+        return out
 
-    def save_checkpoint(self, path, *args, **kwargs) -> dict:
+    def save_checkpoint(self, path, include_batches: bool = True, *, current_batches=None, stage_timings=None,
+                        stage_event_log=None, host_sync_events=None, device_snapshot_log=None,
+                        dataset_state=None) -> dict:
+        state = self.state_dict(current_batches=current_batches, include_batches=include_batches,
+                                stage_timings=stage_timings, stage_event_log=stage_event_log,
+                                host_sync_events=host_sync_events, device_snapshot_log=device_snapshot_log,
+                                dataset_state=dataset_state)
         os.makedirs(path, exist_ok=True)
-        state = self.state_dict()
         with open(os.path.join(path, "state.json"), "w", encoding="utf-8") as f:
-            json.dump(state, f)
+            json.dump(state["payload"], f, indent=2, sort_keys=True)
+        torch.save({k: v.detach().clone().cpu() for k, v in state["tensors"].items()},
+                   os.path.join(path, "tensors.pt"))
         return state
 
-    def load_checkpoint(self, path, *args, **kwargs) -> dict:
+    def load_checkpoint(self, path) -> dict:
+        """Read ``state.json`` / ``tensors.pt`` of a checkpoint directory and return them as
+        ``{"payload", "tensors"}`` for ``fit(resume_state=...)``; nothing is applied here
+        (``bpe_trainer.py:1938-1948``)."""
         with open(os.path.join(path, "state.json"), encoding="utf-8") as f:
-            state = json.load(f)
-        self.load_state_dict(state)
-        return state
+            payload = json.load(f)
+        tensors: dict = {}
+        tp = os.path.join(path, "tensors.pt")
+        if os.path.exists(tp):
+            loaded = torch.load(tp, map_location="cpu")
+            if isinstance(loaded, dict):
+                tensors = loaded
+        return {"payload": payload, "tensors": tensors}
+
+    def export_tokenizer(self, out_dir: str | None = None) -> GPUBPETokenizer:
+        """A runtime tokenizer for the learned merges (``bpe_trainer.py:4758-4773``); with ``out_dir``
+        the artifacts are written there first and the tokenizer is loaded from ``tokenizer.json``."""
+        if out_dir is not None:
+            return GPUBPETokenizer.from_file(self.save_artifacts(out_dir)["tokenizer"])
+        _, _, config, _ = build_artifacts(self.base_vocab, self.merges, self.vocab_size)
+        return GPUBPETokenizer.from_config(config)
 
     def save_artifacts(self, out_dir) -> dict:
         extra: dict = {"privacy": self._privacy_summary()}
@@ -553,4 +803,4 @@ class GPUBPETrainer(BaseTrainer):
               f"{p['vocab']}, {p['merges']}, {p['tokenizer']}, {p['tiktoken_merges']}")
 
 
-__all__ = ["GPUBPETrainer", "StageTiming", "hash_merge_pair"]
+__all__ = ["GPUBPETokenizer", "GPUBPETrainer", "StageTiming", "hash_merge_pair"]

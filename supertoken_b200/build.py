@@ -9,14 +9,17 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libstbpe.so")
 SOURCES = ["engine.cu", "rows_ops.cu"]
-HEADERS = ["common.cuh", "kernels.cuh", os.path.join("..", "..", "include", "stbpe.h")]
+INCLUDE = os.path.join(HERE, "..", "include")
 
 
 def _stale() -> bool:
+    """True when the library is missing or older than any file under csrc/ or include/."""
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    return any(os.path.getmtime(os.path.join(CSRC, f)) > t for f in SOURCES + HEADERS)
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + \
+           [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
+    return any(os.path.getmtime(f) > t for f in deps)
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

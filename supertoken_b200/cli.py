@@ -8,6 +8,10 @@ unchanged, optional BOS / EOS ids are added per row (``gpu_tokenizer/cpu_packer.
 trainer's artifacts are written to ``--out-dir``.  Flags that steer parts of the reference outside
 the merge loop (streaming workers, autoscaler targets, morphology, code mode, augmentation) are
 accepted so that existing command lines keep parsing; they do not influence the merges.
+``--warm-start`` names a JSON manifest or TikToken bundle of seed merges that are applied before the
+loop (``main.py:2351-2356``, loader ``:501-575``); ``--checkpoint-dir`` / ``--checkpoint-every`` write
+``state.json`` + ``tensors.pt`` during training and ``--resume-from`` continues from such a directory
+(``main.py:1397-1571``).
 """
 from __future__ import annotations
 
@@ -40,10 +44,12 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--checkpoint-every", type=int, default=None)
     p.add_argument("--resume-from", default=None)
     p.add_argument("--dry-run", action="store_true")
+    p.add_argument("--warm-start", type=str, default=None,
+                   help="JSON manifest or TikToken bundle containing seed merges")
     # accepted for command-line compatibility; outside the merge loop
     for flag, kw in (("--target-util", dict(type=float, default=0.9)), ("--min-batch", dict(type=int, default=1)),
                      ("--max-batch", dict(type=int, default=65536)), ("--token-bytes", dict(type=int, default=8192)),
-                     ("--warm-start", dict(type=int, default=0)), ("--compression", dict(default=None)),
+                     ("--compression", dict(default=None)),
                      ("--io-workers", dict(type=int, default=1)), ("--prefetch-batches", dict(type=int, default=2)),
                      ("--prefetch-jitter", dict(type=float, default=0.0)), ("--code-mode", dict(action="store_true")),
                      ("--code-langs", dict(nargs="*", default=None)), ("--meta-compress", dict(action="store_true")),
@@ -92,11 +98,21 @@ def main(argv=None) -> int:
     data, off = load_rows(paths, args.bos, args.eos)
     trainer = GPUBPETrainer(base_vocab=args.base_vocab, merges=args.merges, device=args.device,
                             privacy_mode=args.privacy, tie_seed=args.tie_seed, privacy_salt=args.privacy_salt)
+    from .export import load_warm_start_merges
+    warm = load_warm_start_merges(args.warm_start)
+    resume_state = None
     if args.resume_from:
-        trainer.load_checkpoint(args.resume_from)
-        trainer._seed_warm_start_merges = list(trainer.merges)
+        resume_state = trainer.load_checkpoint(args.resume_from)
+        model = resume_state["payload"].get("trainer", {}).get("model", {})
+        print(f"[checkpoint] Restored checkpoint from {args.resume_from} at merge {model.get('merge_step')}")
+        if model.get("target_merges") is not None and int(model["target_merges"]) != int(args.merges):
+            # the reference refuses to resume towards another target (main.py:1465-1483)
+            print("[checkpoint] Error: CLI --merges does not match checkpoint target_merges", file=sys.stderr)
+            return 2
+    every = args.checkpoint_every if args.checkpoint_dir else None
     if data.dtype == np.uint8:
-        trainer.fit_bytes(data, off, log_every=args.log_every)
+        trainer.fit_bytes(data, off, log_every=args.log_every, warm_start_merges=warm,
+                          checkpoint_interval=every, checkpoint_dir=args.checkpoint_dir, resume_state=resume_state)
     else:
         import torch
         L = int(np.diff(off).max()) if len(off) > 1 else 1
@@ -107,7 +123,8 @@ def main(argv=None) -> int:
             tokens[r, :n] = torch.from_numpy(data[off[r]:off[r + 1]])
             valid[r, :n] = 1
         trainer.fit([(tokens, valid, valid.sum(dim=1).to(torch.int32))], log_every=args.log_every,
-                    checkpoint_interval=args.checkpoint_every, checkpoint_dir=args.checkpoint_dir)
+                    warm_start_merges=warm, checkpoint_interval=every, checkpoint_dir=args.checkpoint_dir,
+                    resume_state=resume_state)
     if args.checkpoint_dir:
         trainer.save_checkpoint(args.checkpoint_dir)
     trainer.save(args.out_dir)

@@ -56,7 +56,9 @@ struct __align__(16) TileRec {
 };
 
 struct DevState {
-    int cur_a, cur_b, cur_new, pad0;
+    int cur_a, cur_b, cur_new;
+    int filter_valid;          // the pair filter describes the stream: merges maintain it and skip tiles by it;
+                               // 0 = stale (every merge visits every tile and leaves the filter alone)
     i64 cur_count;
     int merges_done, target, base_vocab, stopped;
     int stop_reason;
@@ -80,6 +82,8 @@ struct DevState {
     int pad2;
     int exchange_only;         // multi-GPU: deltas still in flight, the next round only exchanges
     int round_incomplete;      // multi-GPU: this rank saw a full chunk or kept entries this round
+    u64 tile_bytes_in;         // merge kernel: bytes its bulk copies and record look-ups brought in ...
+    u64 tile_bytes_out;        // ... and bytes it stored (rewritten tile parts and records), since the load
 };
 
 // Peer mailboxes (multi-GPU exchange over NVLink peer memory, no library collective).  Every rank owns
@@ -284,15 +288,24 @@ __device__ __forceinline__ unsigned int hash32(u64 key) {
     return h;
 }
 
-// pair filter: the three rows of a pair key, and setting the pair's bits for a tile.  With about a
+// pair filter: the three rows of a pair key, and setting the pair's bits for a tile.  The filter is
+// kept only while it pays: a merge with more matches than tiles visits nearly every tile anyway, and
+// entering its new pairs costs more than the whole rewrite (measured: 37 of 61 ms on the first 20
+// merges of a 1 GiB corpus), so the host lets the filter go stale for such merges and rebuilds it
+// from the stream once the counts have fallen below the number of tiles.  With about a
 // thousand distinct pairs in a full tile, three bits per pair over 16 384 rows leave a row about 17 %
 // full and let through about 0.5 % of the tiles that do not hold the pair (two bits over 8 192 rows
 // let through 5 %, which late in a run was most of the tiles a merge visited).
 __device__ __forceinline__ void filter_rows(u64 key, unsigned int &r1, unsigned int &r2, unsigned int &r3) {
-    const u64 h = mix64(key);
-    r1 = (unsigned int)h & (STBPE_PROWS - 1);
-    r2 = (unsigned int)(h >> 20) & (STBPE_PROWS - 1);
-    r3 = (unsigned int)(h >> 40) & (STBPE_PROWS - 1);
+    // 32-bit arithmetic only (a 64-bit finaliser costs about three times the instructions, and the
+    // merge kernel hashes two keys per match): two rows from disjoint bits of one mixed word, the
+    // third from a second multiplicative mix of it
+    const unsigned int h = hash32(key);
+    unsigned int g = h * 0x9E3779B1u;
+    g ^= g >> 15;
+    r1 = h & (STBPE_PROWS - 1);
+    r2 = (h >> 14) & (STBPE_PROWS - 1);
+    r3 = (g >> 9) & (STBPE_PROWS - 1);
 }
 __device__ __forceinline__ void filter_set(const EngineDev &e, int tile, u64 key) {
     if (tile < 0) return;
@@ -330,12 +343,17 @@ __device__ __noinline__ void smem_table_add_probe(SmemTable t, const EngineDev *
 // A key never leaves its slot once written, so a plain load that sees the key is final; any
 // other value (empty or a different key) goes to the probing path.  Keeping the fast path free
 // of volatile accesses lets several independent adds overlap.
+__device__ __forceinline__ u64 lds_u64(const u64 *p) {
+    u64 v;
+    asm("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return v;
+}
 template <bool MG>
 __device__ __forceinline__ void smem_table_add(const SmemTable &t, const EngineDev &e, u64 key,
                                                int delta) {
     const unsigned int h = hash32(key) & t.mask;
-    if (t.keys[h] == key)
-        atomicAdd(&t.vals[h], delta);
+    if (lds_u64(&t.keys[h]) == key)
+        reds_add_s32(&t.vals[h], delta);
     else
         smem_table_add_probe<MG>(t, &e, key, delta, h);
 }

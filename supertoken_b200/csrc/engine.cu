@@ -5,7 +5,6 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
-#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -31,6 +30,8 @@ struct stbpe_engine {
     unsigned int merge_slots, count_slots;
     size_t merge_smem, count_smem;
     bool recs_stale, counted;
+    bool filter_valid;    // host mirror of DevState::filter_valid
+    double filter_density;  // the filter is kept while (matches of the last merge) <= filter_density x tiles
     u64 *dense;           // 65 536 global counters of the byte-level count path
     unsigned int *big;    // 2^32 directly indexed counters of the 16-bit-vocabulary count path (lazy)
     i64 dense32_min;      // streams shorter than this use the general kernel
@@ -49,6 +50,7 @@ struct stbpe_engine {
     void *rp_tmp;
     size_t rp_tmp_bytes;
     int repacks;
+    int repacks_since_load;
     cudaGraphExec_t graph;
     int graph_merges;
     uint32_t *graph_tiles;
@@ -144,6 +146,7 @@ static int reset_state(stbpe_engine *e, cudaStream_t s) {
     e->recs_stale = true;
     e->counted = false;
     e->only_bytes = true;
+    e->filter_valid = false;
     return STBPE_OK;
 }
 
@@ -163,6 +166,7 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->rp_tmp = nullptr;
     e->rp_tmp_bytes = 0;
     e->repacks = 0;
+    e->repacks_since_load = 0;
     e->count_ms = 0.f;
     e->convert_ms = 0.f;
     e->ev0 = e->ev1 = nullptr;
@@ -176,6 +180,9 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     memset(e->mail_mapped, 0, sizeof(e->mail_mapped));
     e->peers_open = false;
     e->use_graph = getenv("STBPE_NO_GRAPH") == nullptr;
+    e->filter_valid = false;
+    e->filter_density = 1.0;
+    if (const char *v = getenv("STBPE_FILTER_DENSITY")) e->filter_density = atof(v);
     memset(&e->d, 0, sizeof(e->d));
     auto bail = [&](int code) {
         g_create_err = e->err;
@@ -310,6 +317,15 @@ static int append_common(stbpe_engine *e, const void *data, i64 n, size_t elem, 
         return fail(e, STBPE_E_CAPACITY, "token stream capacity exceeded");
     CK(cudaSetDevice(e->cfg.device));
     if (n == 0) return STBPE_OK;
+    if (!e->recs_stale && e->n_tokens > 0) {
+        // the stream has been counted: appending is still fine while no merge has rewritten a tile
+        // (the tiles are dense and n_tokens is their true length), not afterwards
+        DevState h;
+        CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+        CK(cudaStreamSynchronize(s));
+        if (h.merges_done > 0 || e->repacks_since_load > 0)
+            return fail(e, STBPE_E_STATE, "rows cannot be appended after a merge has been applied; call stbpe_reset first");
+    }
     const void *src = data;
     void *staged = nullptr;
     if (!is_device_pointer(data)) {
@@ -401,18 +417,22 @@ static int prepare_stream_state(stbpe_engine *e, cudaStream_t s) {
         CK(cudaMemcpyAsync(e->d.st, &h, sizeof(h), cudaMemcpyHostToDevice, s));
         CK(cudaStreamSynchronize(s));
         e->recs_stale = false;
+        e->repacks_since_load = 0;
+        e->filter_valid = false;  // a fresh stream starts without a pair filter (see filter_policy)
     }
     return STBPE_OK;
 }
 
-__global__ void clear_skip_state_kernel(EngineDev e) {
+__global__ void clear_skip_state_kernel(EngineDev e, int valid) {
     e.st->n_work = 0;  // a merge that is committed but not yet applied builds its worklist from here
+    e.st->filter_valid = valid;
 }
 
-// presence bitmaps follow the tile layout: rebuilt after a load and after every re-pack
+// The pair filter follows the tile layout: it is rebuilt from the stream, or declared stale.
 static int rebuild_presence(stbpe_engine *e, cudaStream_t s) {
-    clear_skip_state_kernel<<<1, 1, 0, s>>>(e->d);
+    clear_skip_state_kernel<<<1, 1, 0, s>>>(e->d, 1);
     CK(cudaGetLastError());
+    e->filter_valid = true;
     if (e->d.n_tiles > 0) {
         CK(cudaFuncSetAttribute(presence_rebuild_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 STBPE_PROWS * (int)sizeof(unsigned int)));
@@ -427,10 +447,6 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
     e->convert_ms = 0.f;
     int rc = prepare_stream_state(e, s);
     if (rc != STBPE_OK) return rc;
-    if (fresh) {
-        rc = rebuild_presence(e, s);
-        if (rc != STBPE_OK) return rc;
-    }
     clear_table_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
     CK(cudaMemsetAsync(e->d.dirty_flag, 0, e->d.n_blocks * sizeof(unsigned int), s));
@@ -573,6 +589,8 @@ STBPE_VISIBLE int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *cou
     return STBPE_OK;
 }
 
+static int filter_policy(stbpe_engine *e, const DevState &h, bool layout_changed, cudaStream_t s);
+
 static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s) {
     if (e->d.n_tiles > 0) {
         const int wl_words = (e->d.n_tiles + 31) / 32;
@@ -605,6 +623,13 @@ STBPE_VISIBLE int stbpe_apply_merge(stbpe_engine *e, int32_t a, int32_t b, int32
     if (h.merges_done >= e->cfg.max_merges) return fail(e, STBPE_E_CAPACITY, "merge log full");
     force_merge_kernel<<<1, 1, 0, s>>>(e->d, a, b, new_id);
     CK(cudaGetLastError());
+    // the count the table held for (a, b) decides whether this merge keeps the pair filter
+    CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    {
+        int rc = filter_policy(e, h, false, s);
+        if (rc != STBPE_OK) return rc;
+    }
     int rc = launch_merge(e, false, s);
     if (rc != STBPE_OK) return rc;
     rc = launch_refresh(e, 0, s);
@@ -615,19 +640,38 @@ STBPE_VISIBLE int stbpe_apply_merge(stbpe_engine *e, int32_t a, int32_t b, int32
     return check_device_error(e, s);
 }
 
-// Dense re-pack of the stream when at most three quarters of the tile capacity in use is live.
-// Synchronises the stream.  *did (may be NULL) tells whether a re-pack happened.
+// Keep or drop the pair filter.  A merge whose matches outnumber the tiles visits nearly every tile
+// whatever the filter says, while entering its new pairs into the filter costs more than the
+// rewrite itself; so the filter is left stale (every merge visits every tile) until the count of the
+// last selected pair has fallen to filter_density x tiles, and is then rebuilt from the stream and
+// maintained by every later merge.  `h` is the device state as the host has just read it; with
+// `layout_changed` the tiles have moved (re-pack), so a filter that is kept must be rebuilt.
+static int filter_policy(stbpe_engine *e, const DevState &h, bool layout_changed, cudaStream_t s) {
+    if (e->d.n_tiles < 1) return STBPE_OK;
+    i64 cnt = h.merges_done > 0 ? h.cur_count : h.peek_count;  // last selected pair, else the best pair of the count
+    cnt /= e->cfg.world_size;  // the count is global, the tiles are this rank's
+    const bool want = (double)cnt <= e->filter_density * (double)e->d.n_tiles;
+    if (want && (!e->filter_valid || layout_changed)) return rebuild_presence(e, s);
+    if (layout_changed) {
+        clear_skip_state_kernel<<<1, 1, 0, s>>>(e->d, 0);
+        CK(cudaGetLastError());
+        e->filter_valid = false;
+    }
+    return STBPE_OK;
+}
+
+// Maintenance between batches of merges: dense re-pack of the stream when at most three quarters of
+// the tile capacity in use is live, and the pair-filter policy above.  Synchronises the stream.
+// *did (may be NULL) tells whether a re-pack happened.
 static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
     if (did) *did = 0;
     const int nt = e->d.n_tiles;
-    if (nt < 2 || e->recs_stale) return STBPE_OK;
+    if (nt < 1 || e->recs_stale) return STBPE_OK;
     DevState h;
     CK(cudaMemcpyAsync(&h, e->d.st, sizeof(h), cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
-    if (!force && (h.n_live * 4 > (i64)nt * STBPE_TILE * 3 || nt < 64)) return STBPE_OK;  // re-pack at <= 75 % fill
-    const bool dbg = getenv("STBPE_DEBUG_TIMING") != nullptr;
-    auto now = [&]() { cudaStreamSynchronize(s); return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count(); };
-    double t_a = dbg ? now() : 0;
+    if (nt < 2 || (!force && (h.n_live * 4 > (i64)nt * STBPE_TILE * 3 || nt < 64)))  // re-pack at <= 75 % fill
+        return filter_policy(e, h, false, s);
     if (!e->tiles_alt) CK(dev_alloc(e, &e->tiles_alt, (size_t)e->max_tiles * STBPE_TILE));
     i64 *lens = e->rp_lens, *offs = e->rp_offs;
     CK(cudaMemsetAsync(lens + nt, 0, sizeof(i64), s));
@@ -639,10 +683,8 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
     tmp_bytes = e->rp_tmp_bytes;
     cub::DeviceScan::ExclusiveSum(e->rp_tmp, tmp_bytes, lens, offs, nt + 1, s);
     CK(cudaGetLastError());
-    double t_b = dbg ? now() : 0;
     repack_copy_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, offs, e->tiles_alt);
     CK(cudaGetLastError());
-    double t_c = dbg ? now() : 0;
     i64 total = 0;
     CK(cudaMemcpyAsync(&total, offs + nt, sizeof(i64), cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
@@ -655,14 +697,13 @@ static int maybe_repack(stbpe_engine *e, bool force, int *did, cudaStream_t s) {
         init_recs_kernel<<<(e->d.n_tiles + 255) / 256, 256, 0, s>>>(e->d, total);
         CK(cudaGetLastError());
     }
-    double t_d = dbg ? now() : 0;
     {
-        int rc = rebuild_presence(e, s);
+        int rc = filter_policy(e, h, true, s);
         if (rc != STBPE_OK) return rc;
     }
     CK(cudaStreamSynchronize(s));
-    if (dbg) fprintf(stderr, "[repack] scan %.2f copy %.2f recs %.2f filter %.2f ms (tiles %d -> %d)\n", t_b - t_a, t_c - t_b, t_d - t_c, now() - t_d, nt, e->d.n_tiles);
     e->repacks++;
+    e->repacks_since_load++;
     if (did) *did = 1;
     return STBPE_OK;
 }
@@ -706,7 +747,10 @@ STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
     while (todo > 0) {
         int rc = maybe_repack(e, false, nullptr, s);
         if (rc != STBPE_OK) return rc;
-        int batch = todo < CHECK ? todo : CHECK;
+        // while the pair filter is stale the counts are looked at after every graph replay, so that
+        // tile skipping starts soon after it begins to pay
+        const int chk = (e->filter_valid || e->d.n_tiles < 64) ? CHECK : G;
+        int batch = todo < chk ? todo : chk;
         todo -= batch;
         if (e->use_graph && batch >= G) {
             // the kernels take all their work from device state, so one captured batch of G
@@ -785,21 +829,23 @@ STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *ke
     cudaEvent_t r0, r1;
     CK(cudaEventCreate(&r0));
     CK(cudaEventCreate(&r1));
-    for (int base = 0; base < todo && rc == STBPE_OK; base += P) {
-        const int n = todo - base < P ? todo - base : P;
-        if (base % 256 == 0) {
+    for (int base = 0, n = 0; base < todo && rc == STBPE_OK; base += n) {
+        {
             int did = 0;
+            const bool had_filter = e->filter_valid;
             cudaEventRecord(r0, s);
             rc = maybe_repack(e, false, &did, s);
             cudaEventRecord(r1, s);
             cudaEventSynchronize(r1);
-            if (did) {
+            if (did || had_filter != e->filter_valid) {  // a re-pack and / or a rebuild of the pair filter
                 float ms = 0.f;
                 cudaEventElapsedTime(&ms, r0, r1);
                 kernel_ms[3] += ms;
             }
             if (rc != STBPE_OK) break;
         }
+        const int step = (e->filter_valid || e->d.n_tiles < 64) ? P : 32;
+        n = todo - base < step ? todo - base : step;
         for (int i = 0; i < n && rc == STBPE_OK; ++i) {
             cudaEventRecord(ev[4 * i], s);
             select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
@@ -846,6 +892,8 @@ STBPE_VISIBLE int stbpe_get_state(stbpe_engine *e, stbpe_state *out, void *strea
     out->work_tiles = h.n_work;
     out->count_kernel_ms = e->count_ms;
     out->count_convert_ms = e->convert_ms;
+    out->tile_bytes_in = (i64)h.tile_bytes_in;
+    out->tile_bytes_out = (i64)h.tile_bytes_out;
     return STBPE_OK;
 }
 

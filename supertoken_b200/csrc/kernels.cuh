@@ -520,6 +520,10 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
 __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
     DevState *st = e.st;
     if (st->stopped || st->exchange_only) return;
+    if (!st->filter_valid) {  // stale filter: the merge visits every tile
+        if (blockIdx.x == 0 && threadIdx.x == 0) st->n_work = -1;
+        return;
+    }
     unsigned int r1, r2, r3;
     filter_rows(((u64)(uint32_t)st->cur_a << 32) | (u64)(uint32_t)st->cur_b, r1, r2, r3);
     const unsigned int *row1 = e.presence + (size_t)r1 * e.presence_words;

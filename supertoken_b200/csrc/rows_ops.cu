@@ -339,6 +339,16 @@ int static_scratch(unsigned char **out, char *err, size_t err_len) {
         return STBPE_E_CUDA;
     }
     std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev]) {
+        // a cudaDeviceReset since the look-up gives the block a new address: ask again if the cached
+        // one is no longer device memory of this device (a query, no allocation)
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, g_static_ptr[dev]) != cudaSuccess || at.type != cudaMemoryTypeDevice ||
+            at.device != dev) {
+            cudaGetLastError();
+            g_static_ptr[dev] = nullptr;
+        }
+    }
     if (!g_static_ptr[dev]) {
         void *p = nullptr;
         c = cudaGetSymbolAddress(&p, g_static_scratch);
@@ -395,6 +405,8 @@ extern "C" STBPE_VISIBLE int stbpe_rows_count_pairs_noalloc(const int32_t *token
     i64 *scounts = reinterpret_cast<i64 *>(skeys + STBPE_STATIC_MAX_POSITIONS);
     u64 *meta = reinterpret_cast<u64 *>(scounts + STBPE_STATIC_MAX_POSITIONS);
     void *sort_ws = reinterpret_cast<unsigned char *>(meta) + 256;
+    const u64 *sorted_keys = skeys;
+    const i64 *sorted_counts = scounts;
     i64 n = 0;
     if (total > 0) {
         RowsTable t;
@@ -417,22 +429,30 @@ extern "C" STBPE_VISIBLE int stbpe_rows_count_pairs_noalloc(const int32_t *token
             return STBPE_E_CAPACITY;
         }
         if (n > 0) {
-            SCK(cudaMemsetAsync(meta, 0, sizeof(u64), s));
-            rows_export_kernel<<<256, 256, 0, s>>>(t, keys, counts, meta, n);
+            // Sort through double buffers: the two key arrays and the two count arrays of the block are
+            // the sort's ping-pong buffers, so its own workspace holds only digit counters (without
+            // them it would ask for a second copy of keys and counts, 1 MiB at the size limit).  The
+            // workspace size is checked before anything else is queued on the shared block.
+            cub::DoubleBuffer<u64> dk(keys, skeys);
+            cub::DoubleBuffer<i64> dc(counts, scounts);
             size_t need = 0;
-            cub::DeviceRadixSort::SortPairs(nullptr, need, keys, skeys, counts, scounts, (int)n, 0, 64, s);
+            cub::DeviceRadixSort::SortPairs(nullptr, need, dk, dc, (int)n, 0, 64, s);
             if (need > (size_t)STBPE_STATIC_SORT_BYTES) {
                 if (err) snprintf(err, err_len, "sort workspace of %zu bytes exceeds the reserved %d", need, STBPE_STATIC_SORT_BYTES);
                 return STBPE_E_CAPACITY;
             }
-            cub::DeviceRadixSort::SortPairs(sort_ws, need, keys, skeys, counts, scounts, (int)n, 0, 64, s);
+            SCK(cudaMemsetAsync(meta, 0, sizeof(u64), s));
+            rows_export_kernel<<<256, 256, 0, s>>>(t, keys, counts, meta, n);
+            cub::DeviceRadixSort::SortPairs(sort_ws, need, dk, dc, (int)n, 0, 64, s);
             SCK(cudaGetLastError());
+            sorted_keys = dk.Current();
+            sorted_counts = dc.Current();
         }
     }
     if (cap > 0) {
         i64 blocks = (cap + 255) / 256;
         if (blocks > 148 * 32) blocks = 148 * 32;
-        rows_write_kernel<<<(unsigned int)blocks, 256, 0, s>>>(skeys, scounts, n, pair_keys, (i64 *)pair_counts, cap, (i64 *)length_dev);
+        rows_write_kernel<<<(unsigned int)blocks, 256, 0, s>>>(sorted_keys, sorted_counts, n, pair_keys, (i64 *)pair_counts, cap, (i64 *)length_dev);
         SCK(cudaGetLastError());
     } else if (length_dev) {
         SCK(cudaMemsetAsync(length_dev, 0, sizeof(i64), s));

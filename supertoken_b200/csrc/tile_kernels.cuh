@@ -20,16 +20,29 @@
 
 #define STBPE_DERR_TIMEOUT 32u
 #define STBPE_SPIN_LIMIT (1u << 20)
+#ifndef STBPE_NCW
 #define STBPE_NCW 8                              // consumer warps per CTA
+#endif
+#ifndef STBPE_NS
 #define STBPE_NS 16                              // ring stages per CTA
+#endif
+#ifndef STBPE_MIN_CTAS
+#define STBPE_MIN_CTAS 2                         // resident CTAs per SM the kernels are compiled for
+#endif
 // STBPE_NS must be a multiple of STBPE_NCW: then a stage is always consumed by the same warp, and
 // a parity wait can never be more than one phase ahead of its barrier (a waiter that is two
 // phases early would see the older phase of equal parity as "complete" and run onto stale data)
-static_assert(STBPE_NS % STBPE_NCW == 0 && STBPE_NS >= 16, "ring size must be a multiple of the consumer warps");
+static_assert(STBPE_NS % STBPE_NCW == 0 && STBPE_NS >= 8 && STBPE_NCW <= 32, "ring size must be a multiple of the consumer warps");
+#define STBPE_ISSUE_GROUP (STBPE_NS >= 32 ? 32 : (STBPE_NS >= 16 ? 16 : 8))  // producer lanes that issue together
 #define STBPE_CTA_THREADS ((STBPE_NCW + 1) * 32)  // + producer warp
 #define STBPE_CHUNK 128                          // tokens per warp step (4 per lane)
 #define STBPE_QCAP 64                            // per-warp queue of match windows awaiting their delta terms
 #define STBPE_QWORDS 8                           // words per queued window: 6 tokens, tile of the token before the head, own tile
+// A stage holds one tile between two pads of four words: the two live tokens before the tile end
+// the front pad, the three after it follow the tile's last token, so a window around any token of
+// the tile is a run of consecutive shared-memory words.  The tile itself starts 16 bytes into the
+// stage (bulk copies need 16-byte aligned shared-memory addresses).
+#define STBPE_STAGE_WORDS (STBPE_TILE + 8)
 
 struct StageMeta {
     int tile;  // -1 = end of the sequence for the consumer warp that receives it
@@ -101,7 +114,7 @@ struct TilePipe {
 
     __device__ __forceinline__ void carve(unsigned char *base, unsigned int table_slots) {
         tok0 = reinterpret_cast<uint32_t *>(base);
-        unsigned char *p = base + (size_t)STBPE_NS * STBPE_TILE * sizeof(uint32_t);
+        unsigned char *p = base + (size_t)STBPE_NS * STBPE_STAGE_WORDS * sizeof(uint32_t);
         tab.keys = reinterpret_cast<u64 *>(p);
         p += (size_t)table_slots * sizeof(u64);
         tab.vals = reinterpret_cast<int *>(p);
@@ -114,9 +127,9 @@ struct TilePipe {
         p += STBPE_NS * sizeof(StageMeta);
         queue = reinterpret_cast<uint32_t *>(p);
     }
-    __device__ __forceinline__ uint32_t *tok(int stage) const { return tok0 + (size_t)stage * STBPE_TILE; }
+    __device__ __forceinline__ uint32_t *tok(int stage) const { return tok0 + (size_t)stage * STBPE_STAGE_WORDS + 4; }
     static size_t bytes(unsigned int table_slots) {
-        return (size_t)STBPE_NS * STBPE_TILE * sizeof(uint32_t) + (size_t)table_slots * 12 +
+        return (size_t)STBPE_NS * STBPE_STAGE_WORDS * sizeof(uint32_t) + (size_t)table_slots * 12 +
                2 * STBPE_NS * sizeof(uint64_t) + STBPE_NS * sizeof(StageMeta) +
                (size_t)STBPE_NCW * STBPE_QCAP * STBPE_QWORDS * sizeof(uint32_t) + 16;
     }
@@ -161,10 +174,11 @@ __device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe
         }
         const unsigned int has = __ballot_sync(0xFFFFFFFFu, len > 0);
         const int my_it = it_base + __popc(has & lt);
-        // half a warp issues at a time: 16 <= STBPE_NS, so the lanes of a group own distinct stages
-        for (int g = 0; g < 32; g += 16) {
+        // a group of lanes issues at a time: the group is no larger than the ring, so its lanes own
+        // distinct stages
+        for (int g = 0; g < 32; g += STBPE_ISSUE_GROUP) {
             bool ok = true;
-            if (len > 0 && (lane & 16) == g) {
+            if (len > 0 && (lane & ~(STBPE_ISSUE_GROUP - 1)) == g) {
                 const int stage = my_it % STBPE_NS;
                 const uint32_t par = (((uint32_t)(my_it / STBPE_NS)) & 1u) ^ 1u;
                 ok = mbar_wait(&pipe.empty[stage], par, derr);
@@ -214,7 +228,7 @@ __device__ __forceinline__ uint32_t tok_or_halo(const uint32_t *s_tok, const Sta
 // the pair table (or, multi-GPU, into the rank-local delta table).
 // ---------------------------------------------------------------------------------------
 template <bool MG>
-__global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) count_kernel(EngineDev e, unsigned int smem_slots) {
+__global__ void __launch_bounds__(STBPE_CTA_THREADS, STBPE_MIN_CTAS) count_kernel(EngineDev e, unsigned int smem_slots) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     TilePipe pipe;
     pipe.carve(smem_raw, smem_slots);
@@ -365,14 +379,24 @@ __device__ __forceinline__ void drain_queue(const SmemTable &tab, const EngineDe
                                             uint32_t nw, const uint32_t *q, int n, int lane) {
     __syncwarp();
     for (int i = lane; i < n; i += 32) {
-        const uint32_t *d = q + i * STBPE_QWORDS;
-        merge_delta_terms<MG>(tab, e, a, b, nw, d[0], d[1], d[2], d[3], d[4], d[5], (int)d[6], (int)d[7]);
+        const uint4 lo = *reinterpret_cast<const uint4 *>(q + i * STBPE_QWORDS);
+        const uint4 hi = *reinterpret_cast<const uint4 *>(q + i * STBPE_QWORDS + 4);
+        merge_delta_terms<MG>(tab, e, a, b, nw, lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, (int)hi.z, (int)hi.w);
     }
     __syncwarp();
 }
 
+// One warp, one tile.  The tile sits in shared memory with its halo around it (s[-2], s[-1] = the two
+// live tokens before it, s[len .. len+2] = the three after it).  The warp works in passes over the
+// whole tile instead of chunk by chunk, so that the cross-lane steps are paid once per tile:
+//   1. match heads of all 1024 positions into one 32-bit mask per lane (bit 4c+k = position
+//      128c + 4*lane + k); the dropped positions follow from the masks of the neighbouring lane;
+//   2. per-chunk drop counts packed into bytes and scanned across the lanes once;
+//   3. windows of the positions that own delta terms go to the warp's queue (read from the intact
+//      pre-merge tile), then the surviving heads are rewritten in place;
+//   4. chunks at or behind the first drop are re-read and written back compacted.
 template <bool MG>
-__global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e, unsigned int smem_slots) {
+__global__ void __launch_bounds__(STBPE_CTA_THREADS, STBPE_MIN_CTAS) merge_kernel(EngineDev e, unsigned int smem_slots) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DevState *st = e.st;
     if (st->stopped || st->exchange_only) return;
@@ -386,11 +410,14 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
     pipe_setup(pipe);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_work = st->n_work;  // < 0: every tile
+    const bool fv = st->filter_valid != 0;  // the pair filter is being maintained
     if (warp == STBPE_NCW) {
         produce_tiles(e, pipe, m, lane, n_work);
     } else {
         unsigned int *derr = &st->error;
-        i64 removed = 0, matches = 0;
+        i64 removed = 0;
+        int matches = 0;
+        i64 bytes_in = 0, bytes_out = 0;  // lane 0: bulk-copy bytes of this warp's tiles (statistics)
         int pending = -1;  // lane 0: stage whose bulk store may still be reading shared memory
         uint32_t *queue = pipe.queue + (size_t)warp * STBPE_QCAP * STBPE_QWORDS;
         int qn = 0;  // warp-uniform
@@ -406,131 +433,160 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
             const StageMeta *mp = &pipe.meta[stage];
             const int tile = mp->tile;
             if (tile < 0) break;
-            uint32_t *s_tok = pipe.tok(stage);
+            uint32_t *s = pipe.tok(stage);
             const int len = mp->len;
-            int base = 0;          // tokens written so far (compacted in place)
-            bool changed = false;  // warp-uniform
-            bool any_head = false, last_head = false;  // warp-uniform
-            // does the first token of the next chunk vanish (its left neighbour heads a match)?
-            bool carry_drop = ((mp->prev & STBPE_IDMASK) == a) && (s_tok[0] == b);
-            uint32_t pw4 = mp->prev2, pw5 = mp->prev;  // this lane's tokens 2,3 of the previous chunk (pre-merge)
-            for (int cq = 0; cq < len; cq += STBPE_CHUNK) {
-                const int q0 = cq + lane * 4;
-                const uint4 raw = *reinterpret_cast<const uint4 *>(s_tok + q0);
-                uint32_t w[9];  // pre-merge window: positions q0-2 .. q0+6
-                w[2] = raw.x, w[3] = raw.y, w[4] = raw.z, w[5] = raw.w;
-                const bool whole = (cq + STBPE_CHUNK <= len);  // warp-uniform
-                unsigned int valid = 0xFu;                      // which of my 4 positions are in the tile
-                if (!whole) {
-                    valid = 0;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        if (q0 + k < len) valid |= 1u << k;
-                        else w[2 + k] = tok_or_halo(s_tok, mp, len, q0 + k);
-                    }
-                }
-                // cheap test first: does any match start in this chunk?  Comparing the whole word of
-                // a right-hand token with b also checks that it does not start a row.
-                w[6] = __shfl_down_sync(0xFFFFFFFFu, w[2], 1);
-                if (lane == 31) w[6] = tok_or_halo(s_tok, mp, len, cq + STBPE_CHUNK);
-                unsigned int heads = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (((w[2 + k] & STBPE_IDMASK) == a) && (w[3 + k] == b)) heads |= 1u << k;
-                heads &= valid;
-                const int nvalid = min(STBPE_CHUNK, len - cq);
-                if (__ballot_sync(0xFFFFFFFFu, heads != 0u) == 0u && !carry_drop) {
-                    // nothing here matches or vanishes: keep, or slide left behind earlier drops
-                    if (base != cq) {
-                        __syncwarp();
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if ((valid >> k) & 1u) s_tok[base + lane * 4 + k] = w[2 + k];
-                    }
-                    base += nvalid;
-                    pw4 = w[4], pw5 = w[5];
-                    continue;
-                }
-                // full window: neighbours across lanes
-                w[0] = __shfl_up_sync(0xFFFFFFFFu, w[4], 1);
-                w[1] = __shfl_up_sync(0xFFFFFFFFu, w[5], 1);
-                w[7] = __shfl_down_sync(0xFFFFFFFFu, w[3], 1);
-                w[8] = __shfl_down_sync(0xFFFFFFFFu, w[4], 1);
-                {
-                    const uint32_t c2 = __shfl_sync(0xFFFFFFFFu, pw4, 31), c1 = __shfl_sync(0xFFFFFFFFu, pw5, 31);
-                    if (lane == 0) {
-                        w[0] = cq ? c2 : mp->prev2;
-                        w[1] = cq ? c1 : mp->prev;
-                    }
-                }
-                if (lane == 31) {
-                    w[7] = tok_or_halo(s_tok, mp, len, cq + STBPE_CHUNK + 1);
-                    w[8] = tok_or_halo(s_tok, mp, len, cq + STBPE_CHUNK + 2);
-                }
-                uint32_t out[4];
-                unsigned int keep = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    out[k] = w[2 + k];
-                    bool owns = false;
-                    if ((valid >> k) & 1u) {
-                        const uint32_t t0 = w[2 + k];
-                        const bool M0 = (heads >> k) & 1u;
-                        const bool D0 = (t0 == b) && ((w[1 + k] & STBPE_IDMASK) == a);
-                        if (M0) out[k] = nw | (t0 & STBPE_FLAG);
-                        if (!D0) keep |= 1u << k;
-                        matches += (int)M0;
-                        owns = same ? (M0 != D0) : M0;  // match head (a != b) or run head / tail (a == b)
-                    }
-                    const unsigned int om = __ballot_sync(0xFFFFFFFFu, owns);
-                    if (om) {
-                        if (owns) {
-                            uint32_t *d = queue + (qn + __popc(om & lt)) * STBPE_QWORDS;
-                            d[0] = w[k], d[1] = w[1 + k], d[2] = w[2 + k], d[3] = w[3 + k], d[4] = w[4 + k], d[5] = w[5 + k];
-                            d[6] = (uint32_t)((q0 + k) > 0 ? tile : mp->prev_tile);
-                            d[7] = (uint32_t)tile;
-                        }
-                        qn += __popc(om);
-                        if (qn >= 32) {
-                            drain_queue<MG>(pipe.tab, e, a, b, nw, queue, qn, lane);
-                            qn = 0;
-                        }
-                    }
-                }
-                changed = true;  // a head or a carried drop: the tile is rewritten
-                {
-                    const unsigned int hb = __ballot_sync(0xFFFFFFFFu, heads != 0u);
-                    any_head |= hb != 0u;
-                    const int lastq = len - 1 - cq;  // position of the tile's last token in this chunk
-                    if (lastq >= 0 && lastq < STBPE_CHUNK)
-                        last_head = (__shfl_sync(0xFFFFFFFFu, heads, lastq >> 2) >> (lastq & 3)) & 1u;
-                }
-                // the last position of the chunk heads a match: its partner opens the next chunk
-                carry_drop = ((__ballot_sync(0xFFFFFFFFu, (heads >> 3) & 1u) >> 31) & 1u) && whole;
-                const int cnt = __popc(keep);
-                int incl = cnt;
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const int n = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-                    if (lane >= d) incl += n;
-                }
-                int pos = base + incl - cnt;
-                __syncwarp();  // all lanes hold their window before anyone overwrites the stage
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if ((keep >> k) & 1u) s_tok[pos++] = out[k];
-                base += __shfl_sync(0xFFFFFFFFu, incl, 31);
-                pw4 = w[4], pw5 = w[5];
+            bytes_in += ((len * 4 + 15) & ~15) + 2 * (int)sizeof(TileRec);
+            // halo around the tile (the bulk copy may have written up to three words past len)
+            if (lane == 0) {
+                s[-2] = mp->prev2;
+                s[-1] = mp->prev;
+            } else if (lane <= 3) {
+                s[len + lane - 1] = mp->nxt[lane - 1];
             }
-            if (!changed) {
+            __syncwarp();
+            const int nch = (len + STBPE_CHUNK - 1) / STBPE_CHUNK;
+            // ---- pass 1: match heads.  Comparing the whole word of the right-hand token with b also
+            // checks that it does not start a row.
+            uint32_t hmask = 0;
+#pragma unroll
+            for (int c = 0; c < STBPE_TILE / STBPE_CHUNK; ++c) {
+                if (c < nch) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(s + c * STBPE_CHUNK + lane * 4);
+                    uint32_t nx = __shfl_down_sync(0xFFFFFFFFu, v.x, 1);
+                    if (lane == 31) nx = s[(c + 1) * STBPE_CHUNK];
+                    unsigned int h = 0;
+                    if (((v.x & STBPE_IDMASK) == a) && (v.y == b)) h |= 1u;
+                    if (((v.y & STBPE_IDMASK) == a) && (v.z == b)) h |= 2u;
+                    if (((v.z & STBPE_IDMASK) == a) && (v.w == b)) h |= 4u;
+                    if (((v.w & STBPE_IDMASK) == a) && (nx == b)) h |= 8u;
+                    hmask |= h << (4 * c);
+                }
+            }
+            // positions of this lane that lie inside the tile
+            const int cf = len / STBPE_CHUNK;  // full chunks
+            uint32_t vmask = 0xFFFFFFFFu;
+            if (cf < STBPE_TILE / STBPE_CHUNK) {
+                const int rem = min(4, max(0, len - cf * STBPE_CHUNK - lane * 4));
+                vmask = ((1u << (4 * cf)) - 1u) | (((1u << rem) - 1u) << (4 * cf));
+            }
+            hmask &= vmask;
+            // a position is dropped when the position before it heads a match: inside the lane a shift
+            // of the mask, at the lane's first token the last token of the lane before it, and for
+            // lane 0 the last token of lane 31 in the chunk before (the tile's first token: the halo)
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, hmask, 1);
+            const uint32_t h31 = __shfl_sync(0xFFFFFFFFu, hmask, 31);
+            uint32_t top = (up >> 3) & 0x11111111u;
+            if (lane == 0) {
+                const bool carry_in = ((mp->prev & STBPE_IDMASK) == a) && (s[0] == b);
+                top = (((h31 >> 3) & 0x01111111u) << 4) | (carry_in ? 1u : 0u);
+            }
+            const uint32_t drops = (((hmask << 1) & 0xEEEEEEEEu) | top) & vmask;
+            const uint32_t touched = hmask | drops;
+            if (__ballot_sync(0xFFFFFFFFu, touched != 0u) == 0u) {  // the filter let a tile through in vain
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&pipe.empty[stage]);
                 continue;
             }
-            const int newlen = base;
+            matches += __popc(hmask);
+            const int lastq = len - 1;
+            const bool last_head =
+                (__shfl_sync(0xFFFFFFFFu, hmask, (lastq & (STBPE_CHUNK - 1)) >> 2) >> (4 * (lastq / STBPE_CHUNK) + (lastq & 3))) & 1u;
+            // first position whose word changes (bit order inside a lane is position order)
+            int firstq = 0x7FFFFFFF;
+            if (touched) {
+                const int bit = __ffs(touched) - 1;
+                firstq = (bit >> 2) * STBPE_CHUNK + lane * 4 + (bit & 3);
+            }
+            firstq = __reduce_min_sync(0xFFFFFFFFu, firstq);
+
+            // ---- pass 2: drops before every position.  Per-chunk drop counts of this lane as bytes
+            // (even chunks in `lo`, odd chunks in `hi`; a chunk holds at most 128 drops), one
+            // inclusive scan over the lanes for all eight chunks.
+            uint32_t own_lo, own_hi, inc_lo, inc_hi;
+            {
+                uint32_t x = drops - ((drops >> 1) & 0x55555555u);
+                x = (x & 0x33333333u) + ((x >> 2) & 0x33333333u);  // drops per nibble
+                own_lo = x & 0x0F0F0F0Fu;
+                own_hi = (x >> 4) & 0x0F0F0F0Fu;
+                inc_lo = own_lo, inc_hi = own_hi;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const uint32_t nl = __shfl_up_sync(0xFFFFFFFFu, inc_lo, d);
+                    const uint32_t nh = __shfl_up_sync(0xFFFFFFFFu, inc_hi, d);
+                    if (lane >= d) {
+                        inc_lo += nl;
+                        inc_hi += nh;
+                    }
+                }
+            }
+            const uint32_t tot_lo = __shfl_sync(0xFFFFFFFFu, inc_lo, 31), tot_hi = __shfl_sync(0xFFFFFFFFu, inc_hi, 31);
+            const uint32_t exc_lo = inc_lo - own_lo, exc_hi = inc_hi - own_hi;  // drops in lanes before this one
+            int cb[STBPE_TILE / STBPE_CHUNK + 1];  // drops before chunk c (warp-uniform)
+            cb[0] = 0;
+#pragma unroll
+            for (int c = 0; c < STBPE_TILE / STBPE_CHUNK; ++c)
+                cb[c + 1] = cb[c] + (int)((((c & 1) ? tot_hi : tot_lo) >> (8 * (c >> 1))) & 0xFFu);
+            const int newlen = len - cb[STBPE_TILE / STBPE_CHUNK];
+
+            // ---- pass 3: windows of the positions that own delta terms (match heads when a != b; the
+            // first and the last token of a run of equal tokens when a == b), one per lane and round
+            {
+                uint32_t owners = same ? (hmask ^ drops) : hmask;
+                for (;;) {
+                    const unsigned int om = __ballot_sync(0xFFFFFFFFu, owners != 0u);
+                    if (om == 0u) break;
+                    if (owners) {
+                        const int bit = __ffs(owners) - 1;
+                        owners &= owners - 1u;
+                        const int q = (bit >> 2) * STBPE_CHUNK + lane * 4 + (bit & 3);
+                        const uint32_t *w = s + q - 2;
+                        uint4 lo, hi;
+                        lo.x = w[0], lo.y = w[1], lo.z = w[2], lo.w = w[3];
+                        hi.x = w[4], hi.y = w[5];
+                        // tiles whose filter bits the new pairs go into; -1 (no tile) while the filter is stale
+                        hi.z = (uint32_t)(fv ? (q > 0 ? tile : mp->prev_tile) : -1);
+                        hi.w = (uint32_t)(fv ? tile : -1);
+                        uint32_t *d = queue + (qn + __popc(om & lt)) * STBPE_QWORDS;
+                        *reinterpret_cast<uint4 *>(d) = lo;
+                        *reinterpret_cast<uint4 *>(d + 4) = hi;
+                    }
+                    qn += __popc(om);
+                    if (qn >= 32) {
+                        drain_queue<MG>(pipe.tab, e, a, b, nw, queue, qn, lane);
+                        qn = 0;
+                    }
+                }
+            }
+            __syncwarp();  // every window has been read: the tile may change now
+            {   // surviving heads become the new token (the row-start flag stays)
+                uint32_t pm = hmask & ~drops;
+                while (pm) {
+                    const int bit = __ffs(pm) - 1;
+                    pm &= pm - 1u;
+                    const int q = (bit >> 2) * STBPE_CHUNK + lane * 4 + (bit & 3);
+                    s[q] = nw | (s[q] & STBPE_FLAG);
+                }
+            }
+            __syncwarp();
+            // ---- pass 4: compaction.  Chunks in front of the first drop stay where they are.
+            const uint32_t keepm = vmask & ~drops;
+#pragma unroll
+            for (int c = 0; c < STBPE_TILE / STBPE_CHUNK; ++c) {
+                if (c < nch && cb[c + 1] != 0) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(s + c * STBPE_CHUNK + lane * 4);
+                    __syncwarp();  // all lanes hold their tokens before anyone overwrites the chunk
+                    const unsigned int keep = (keepm >> (4 * c)) & 15u;
+                    const int before = cb[c] + (int)((((c & 1) ? exc_hi : exc_lo) >> (8 * (c >> 1))) & 0xFFu);
+                    uint32_t *o = s + c * STBPE_CHUNK + lane * 4 - before;
+                    if (keep & 1u) *o++ = v.x;
+                    if (keep & 2u) *o++ = v.y;
+                    if (keep & 4u) *o++ = v.z;
+                    if (keep & 8u) *o++ = v.w;
+                }
+            }
             fence_async_smem();  // the bulk store reads these writes through the async proxy
             __syncwarp();
-            if (same && last_head && lane == 0) {
+            if (fv && same && last_head && lane == 0) {
                 // the run of a's goes on in the next tile: the pair that will start at the collapsed
                 // token is decided by whoever finds the run's tail, so visit this tile from now on
                 unsigned int *p = e.presence + (size_t)STBPE_PROWS * e.presence_words + ((unsigned int)tile >> 5);
@@ -550,37 +606,43 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, 2) merge_kernel(EngineDev e
                         if (same && !(y & STBPE_FLAG)) {
                             smem_table_add<MG>(pipe.tab, e, ((u64)a << 32) | (u64)y, -1);
                             smem_table_add<MG>(pipe.tab, e, ((u64)nw << 32) | (u64)y, 1);
-                            filter_set(e, tile, ((u64)nw << 32) | (u64)y);
+                            if (fv) filter_set(e, tile, ((u64)nw << 32) | (u64)y);
                         }
                     }
                 }
             }
             if (lane == 0) {
-                if (newlen > 0) {
-                    tma_store_1d(e.tiles + (i64)tile * STBPE_TILE, s_tok, ((uint32_t)newlen * 4u + 15u) & ~15u);
+                // only the part of the tile from the first changed word on goes back to HBM
+                const int start = firstq & ~3;
+                if (newlen > start) {
+                    tma_store_1d(e.tiles + (i64)tile * STBPE_TILE + start, s + start,
+                                 ((uint32_t)(newlen - start) * 4u + 15u) & ~15u);
                     tma_commit();
                     pending = stage;
+                    bytes_out += ((newlen - start) * 4 + 15) & ~15;
                 }
+                bytes_out += (int)sizeof(TileRec);
                 // the record that is not current before this merge; readers of this merge never pick a
                 // record stamped m, so payload and stamp need no ordering between them
                 TileRec *dst = &e.recs[2 * tile + (mp->slot ^ 1)];
                 dst->len = newlen;
-                for (int i = 0; i < 3; ++i) dst->head[i] = i < newlen ? s_tok[i] : STBPE_NONE;
-                dst->tail = newlen > 0 ? s_tok[newlen - 1] : STBPE_NONE;
-                dst->tail2 = newlen > 1 ? s_tok[newlen - 2] : STBPE_NONE;
+                for (int i = 0; i < 3; ++i) dst->head[i] = i < newlen ? s[i] : STBPE_NONE;
+                dst->tail = newlen > 0 ? s[newlen - 1] : STBPE_NONE;
+                dst->tail2 = newlen > 1 ? s[newlen - 2] : STBPE_NONE;
                 dst->ver = m;
                 removed += len - newlen;
-                if (newlen == 0) mbar_arrive(&pipe.empty[stage]);
+                if (pending != stage) mbar_arrive(&pipe.empty[stage]);
             }
         }
         drain_queue<MG>(pipe.tab, e, a, b, nw, queue, qn, lane);
         if (lane == 0) {
             tma_wait_all();  // bulk stores must have landed before the grid ends
             if (removed) atomicAdd((u64 *)&st->n_live, (u64)(-removed));
+            if (bytes_in) atomicAdd(&st->tile_bytes_in, (u64)bytes_in);
+            if (bytes_out) atomicAdd(&st->tile_bytes_out, (u64)bytes_out);
         }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) matches += __shfl_down_sync(0xFFFFFFFFu, matches, d);
-        if (lane == 0 && matches) atomicAdd((u64 *)&st->n_matches, (u64)matches);
+        matches = __reduce_add_sync(0xFFFFFFFFu, matches);
+        if (lane == 0 && matches) atomicAdd((u64 *)&st->n_matches, (u64)(i64)matches);
     }
     __syncthreads();
     smem_table_flush<MG>(pipe.tab, e);

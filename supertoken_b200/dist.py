@@ -120,6 +120,17 @@ def reduce_pair_histograms(keys: torch.Tensor, counts: torch.Tensor, group=None)
                       torch.cat([c[:m] for c, m in zip(all_c, sizes)]))
 
 
+def rounds_until_next_check(done: int, target: int, check_every: int) -> int:
+    """Rounds to enqueue before the host looks at the device state again.  Every rank must enqueue
+    the same number, so this depends only on what all ranks agree on (merges committed, target).
+    Early in a run the host looks more often: that is where each rank decides to start keeping its
+    pair filter (tile skipping) and to re-pack.  Never more rounds than the target still needs
+    (one per merge plus the round that applies the last one); exchange-only rounds, if any, are
+    caught by the next check."""
+    n = check_every if done >= 512 else min(check_every, 32)
+    return max(1, min(n, target - done + 1))
+
+
 # ----------------------------------------------------------------------------- workers
 class EngineWorker:
     """One rank's engine plus its exchange buffers (torch tensors on the engine's device)."""
@@ -246,7 +257,9 @@ class ShardedBPE:
             done, reason = states[0]
             if reason != L.RUNNING or left <= 0:
                 return done, reason
-            n = min(check_every, left)
+            w0 = self.workers[0]
+            target = w0.max_merges if hasattr(w0, "max_merges") else w0.e.max_merges
+            n = min(rounds_until_next_check(done, target, check_every), left)
             for _ in range(n):
                 self._round(False)
             left -= n
@@ -302,7 +315,7 @@ class NativeLoop:
             done, reason = self.progress()
             if reason != L.RUNNING:
                 return done, reason
-            self.run(check_every)
+            self.run(rounds_until_next_check(done, self.e.max_merges, check_every))
 
 
 class PeerLoop:
@@ -356,7 +369,7 @@ class PeerLoop:
             done, reason = self.progress()
             if reason != L.RUNNING:
                 return done, reason
-            self.run(check_every)
+            self.run(rounds_until_next_check(done, self.e.max_merges, check_every))
 
     def close(self):
         """Unmap the peers' mailboxes and wait for every rank to have done so; only then may a
@@ -480,7 +493,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     finish(e, loop2)
 
     if rank == 0:
-        from bench import peaks  # type: ignore
+        from bench import merges_sha256, peaks  # type: ignore
         peak, peak_kind = peaks()
         algo = 4.0 * float(live_all.item())
         line = {
@@ -490,6 +503,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
             "data": "synthetic",
             "config": {"workload": desc, "name": args.workload, "corpus_bytes": int(tokens_all.item()),
                        "rows": len(off) - 1, "merges_timed": done, "first_merge": 0, "stop_reason": int(stop),
+                       "merges_sha256": merges_sha256(merges_gpu, counts_gpu),
                        "sharding": "contiguous document ranges by bytes; pair keys by hash owner",
                        "rounds": rounds, "chunk_entries": 4096,
                        "round_driver": {"peer": "kernels over NVLink peer memory, CUDA graph of 16 rounds (stbpe_mg_peer_run)",

@@ -11,6 +11,25 @@ from tests.helpers import corpus_rows, learned_prefix, load_golden
 
 pytestmark = pytest.mark.gpu
 
+# The engine keeps its pair filter (tile skipping) only once the selected pair's count has fallen to
+# the number of tiles; small inputs would therefore rarely skip a tile.  Every test here runs twice:
+# with the engine's own policy and with the filter kept from the first merge on (the library reads
+# STBPE_FILTER_DENSITY when an engine is created).  The largest cases run with the policy only.
+_POLICY_ONLY = {"test_config1_full_size_parity", "test_full_size_properties_on_a_256_mib_corpus",
+                "test_wide_dense_count_path_for_16_bit_vocabularies", "test_byte_level_dense_count_path",
+                "test_errors", "test_config3_slice_histogram_parity"}
+
+
+@pytest.fixture(autouse=True, params=["policy", "filter_always"])
+def filter_mode(request, monkeypatch):
+    if request.param == "filter_always":
+        if request.node.originalname in _POLICY_ONLY:
+            pytest.skip("runs with the engine's own filter policy only")
+        monkeypatch.setenv("STBPE_FILTER_DENSITY", "1e30")
+    else:
+        monkeypatch.delenv("STBPE_FILTER_DENSITY", raising=False)
+    return request.param
+
 
 def _hist(e):
     k, c = e.export_histogram()
@@ -238,6 +257,17 @@ def test_errors():
         e.apply_merge(1, 2, 1 << 31)
     with pytest.raises(ValueError):
         e.append_ids(np.array([1, 2], dtype=np.int32), np.array([1, 2], dtype=np.int64))
+    # rows may still be appended after a count, but not once a merge has rewritten the stream
+    e.append_ids(np.array([1, 2, 1, 2], dtype=np.int32))
+    e.count_initial()
+    assert e.select_best()[:2] == ((1 << 32) | 2, 4)
+    e.train(1)
+    with pytest.raises(RuntimeError, match="cannot be appended"):
+        e.append_ids(np.array([1, 2], dtype=np.int32))
+    e.reset()
+    e.append_ids(np.array([5, 5, 5], dtype=np.int32))
+    e.count_initial()
+    assert e.select_best()[:2] == ((5 << 32) | 5, 2)
     e.close()
     # a pair table that is too small reports the reference's capacity error
     rng = np.random.default_rng(0)
@@ -290,7 +320,8 @@ def test_tile_skipping_fixup_for_matches_that_straddle_tiles():
     off = np.array([0, 10, 12 * T + 7, len(ids)], dtype=np.int64)
     e = _engine_for(ids, off, 256, 60)
     assert e.apply_merge(300, 301, 256) == 4   # id 256 = base_vocab + 0, as the loop numbers merges
-    assert e.state().fixups >= 2             # tiles 18 and 31 hold no 300 (5 does: it is visited)
+    assert e.state().fixups >= 2             # tiles 18 and 31 hold no 300 (5 does: it is visited);
+    # four matches in 41 tiles: the policy keeps the filter for this merge too
     ids2, off2 = ids.copy(), off.copy()
     assert O.apply_merge_flat(ids2, off2, 300, 301, 256) == 4
     gi, go = e.export_stream()

@@ -70,3 +70,36 @@ def test_noalloc_rejects_oversized_batches_and_small_buffers():
     s0, k0, c0, n0, _ = _run("stbpe_rows_count_pairs", tokens, valid, 4 * 49)
     s1, k1, c1, n1, _ = _run("stbpe_rows_count_pairs_noalloc", tokens, valid, 4 * 49)
     assert s0 == s1 == _lib.OK and n0 == n1 and torch.equal(k0, k1) and torch.equal(c0, c1)
+
+
+def test_noalloc_at_the_size_limit_with_all_pairs_distinct():
+    # 65 536 pair positions, every pair different: the largest number of unique keys the fixed block
+    # has to sort (its sort runs through the block's own double buffers, whatever the count)
+    tokens = torch.arange(65537, dtype=torch.int32).reshape(1, -1).cuda()
+    valid = torch.ones((1, 65537), dtype=torch.uint8).cuda()
+    cap = 65536
+    s0, k0, c0, n0, _ = _run("stbpe_rows_count_pairs", tokens, valid, cap)
+    s1, k1, c1, n1, msg = _run("stbpe_rows_count_pairs_noalloc", tokens, valid, cap)
+    assert s0 == _lib.OK and s1 == _lib.OK, msg
+    assert n0 == n1 == 65536 and torch.equal(k0, k1) and torch.equal(c0, c1)
+    assert k1[:, 0].tolist() == list(range(65536)) and torch.all(c1 == 1)
+    # a small batch right after it must not see the large one's leftovers
+    tokens, valid = _batch(6, 3, 40, 6)
+    s0, k0, c0, n0, _ = _run("stbpe_rows_count_pairs", tokens, valid, 3 * 39)
+    s1, k1, c1, n1, _ = _run("stbpe_rows_count_pairs_noalloc", tokens, valid, 3 * 39)
+    assert s0 == s1 == _lib.OK and n0 == n1 and torch.equal(k0, k1) and torch.equal(c0, c1)
+
+
+def test_noalloc_against_the_reference_made_fixtures():
+    # the histograms the reference's own count_pairs produced (tests/golden/ops.json)
+    from tests.helpers import load_golden
+    for case in load_golden("ops.json")["count"]:
+        tokens = torch.tensor(case["tokens"], dtype=torch.int32).cuda()
+        valid = torch.tensor(case["valid"], dtype=torch.uint8).cuda()
+        B, L = tokens.shape
+        cap = max(B * max(L - 1, 0), 1)
+        status, keys, counts, n, msg = _run("stbpe_rows_count_pairs_noalloc", tokens, valid, cap)
+        assert status == _lib.OK, msg
+        assert n == len(case["keys"])
+        packed = (keys[:n, 0].to(torch.int64) << 32) | keys[:n, 1].to(torch.int64)
+        assert packed.tolist() == case["keys"] and counts[:n].tolist() == case["counts"]
