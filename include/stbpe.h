@@ -60,9 +60,10 @@ typedef struct stbpe_state {
     int64_t fixups;           /* dropped partners handled outside the visited tiles (statistics) */
     int64_t repacks;          /* dense re-packs of the stream so far */
     int64_t work_tiles;       /* tiles visited by the last merge (after the pair filter) */
-    double count_kernel_ms;   /* device time of the histogram kernel(s) of the last count */
-    double count_convert_ms;  /* 16-bit-vocabulary path only: device time of moving the directly
-                                 indexed counters into the pair table (0 otherwise) */
+    double count_kernel_ms;   /* device time of the histogram kernel(s) of the last count; on the
+                                 16-bit-vocabulary path both passes, i.e. until the pair table is complete */
+    double count_convert_ms;  /* 16-bit-vocabulary path only: the part of count_kernel_ms spent in the
+                                 second pass (per-partition counting and table inserts; 0 otherwise) */
     int64_t tile_bytes_in;    /* merge kernel, since the last load: bytes of tiles and tile records read ... */
     int64_t tile_bytes_out;   /* ... and bytes of rewritten tile parts and records stored (statistics) */
 } stbpe_state;

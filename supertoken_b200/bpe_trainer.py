@@ -327,6 +327,7 @@ class GPUBPETrainer(BaseTrainer):
         events: List[dict] = []
         self.merges = list(already) if already else []
         self.merge_counts = []
+        self._readbacks: List[dict] = []
         self.vocab_size = self.base_vocab + len(self.merges)
         skip = len(self.merges)   # merges the engine's own log does not hold
         if already:
@@ -373,6 +374,9 @@ class GPUBPETrainer(BaseTrainer):
                     timings["host_sync"].record(time.perf_counter() - th)   # merge log back to the host
                     self.bytes_d2h += len(got) * 24
                     self.d2h_events += 1
+                    if got:
+                        self._readbacks.append({"merge": len(self.merges) + len(got) - 1, "merges": len(got),
+                                                "bytes_d2h": len(got) * 24})
                     self.merges.extend(got)
                     self.merge_counts.extend(int(c) for c in counts)
                     self.vocab_size = self.base_vocab + len(self.merges)
@@ -403,9 +407,9 @@ class GPUBPETrainer(BaseTrainer):
         self._last_stats = {"live_tokens": int(st.live_tokens), "table_keys": int(st.table_keys),
                             "table_slots": int(st.table_slots), "loop_s": loop_s,
                             "total_s": time.perf_counter() - t0, "stop_reason": int(reason)}
-        # The loop runs on the device: nothing is copied to the host per merge, the merge log comes
-        # back once per train call (24 bytes per merge: pair, count, live tokens), so there is no
-        # per-merge transfer record to report.
+        # The loop runs on the device: nothing is copied to the host per merge.  The merge log comes
+        # back once per train call (24 bytes per merge: pair, count, live tokens); merge_stats holds
+        # one record per such read-back, named after the last merge it brought.
         n_learned = len(self.merge_counts)
         return {
             "base_vocab": self.base_vocab,
@@ -415,7 +419,7 @@ class GPUBPETrainer(BaseTrainer):
             "transfer_metrics": {
                 "bytes_h2d": self.bytes_h2d, "bytes_d2h": self.bytes_d2h,
                 "h2d_events": self.h2d_events, "d2h_events": self.d2h_events,
-                "merge_stats": [], "sync_intervals": [],
+                "merge_stats": list(getattr(self, "_readbacks", [])), "sync_intervals": [],
                 "per_device": {self.device: {"bytes_h2d": self.bytes_h2d, "bytes_d2h": self.bytes_d2h}},
                 "per_stage": {"pair_count": {"h2d": self.bytes_h2d, "d2h": 0}, "apply_merge": {"h2d": 0, "d2h": 0},
                               "host_sync": {"h2d": 0, "d2h": self.bytes_d2h}},

@@ -37,7 +37,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--base-vocab", type=int, default=256)
     p.add_argument("--log-every", type=int, default=100)
     p.add_argument("--out-dir", default="out")
-    p.add_argument("--privacy", action="store_true")
+    p.add_argument("--privacy", type=str, default="none", choices=["none", "hash-merges", "tie-randomize"])
     p.add_argument("--privacy-salt", default=None)
     p.add_argument("--tie-seed", type=int, default=None)
     p.add_argument("--checkpoint-dir", default=None)
@@ -96,8 +96,10 @@ def main(argv=None) -> int:
         return 0
     from .bpe_trainer import GPUBPETrainer
     data, off = load_rows(paths, args.bos, args.eos)
+    # privacy modes as the reference's factory maps them (main.py:674-689)
     trainer = GPUBPETrainer(base_vocab=args.base_vocab, merges=args.merges, device=args.device,
-                            privacy_mode=args.privacy, tie_seed=args.tie_seed, privacy_salt=args.privacy_salt)
+                            privacy_mode=args.privacy != "none", randomize_ties=args.privacy == "tie-randomize",
+                            tie_seed=args.tie_seed, privacy_salt=args.privacy_salt)
     from .export import load_warm_start_merges
     warm = load_warm_start_merges(args.warm_start)
     resume_state = None

@@ -107,6 +107,7 @@ struct EngineDev {
     int n_tiles;
     Slot *table;
     u64 mask;
+    int slot_bits;  // log2(slots) - STBPE_PART_BITS: slot index bits below the partition
     Slot *blockmax;
     unsigned int *dirty_flag;
     unsigned int *dirty_list;
@@ -157,8 +158,45 @@ __device__ __forceinline__ u64 mix64(u64 x) {
 }
 
 
+// Partition of a pair key: the top STBPE_PART_BITS bits of an invertible 32-bit mix of the key folded
+// to 32 bits (for ids below 65 536 the fold is (a << 16) | b itself, so the mixed word identifies the
+// pair).  One function places a key three ways: the partition is the top bits of its slot in the
+// pair table (so the keys of a partition fill one contiguous slice of the table, which the
+// partitioned first count keeps in L2 while it fills it), it is the partition of that count, and
+// its residue modulo the number of ranks is the rank that owns the key.
+#define STBPE_PART_BITS 8
+#define STBPE_PARTS (1 << STBPE_PART_BITS)
+__host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16;
+    x *= 0x7feb352du;
+    x ^= x >> 15;
+    x *= 0x846ca68bu;
+    x ^= x >> 16;
+    return x;
+}
+__host__ __device__ __forceinline__ uint32_t unmix32(uint32_t x) {  // inverse of mix32
+    x ^= x >> 16;
+    x *= 0x43021123u;
+    x ^= (x >> 15) ^ (x >> 30);
+    x *= 0x1d69e2a5u;
+    x ^= x >> 16;
+    return x;
+}
+__host__ __device__ __forceinline__ uint32_t fold_key(u64 key) {
+    const uint32_t a = (uint32_t)(key >> 32), b = (uint32_t)key;
+    return (a << 16) ^ b ^ ((a >> 16) * 0x9E3779B1u) ^ ((b >> 16) * 0x85EBCA77u);
+}
+__host__ __device__ __forceinline__ unsigned int part_of(u64 key) {
+    return mix32(fold_key(key)) >> (32 - STBPE_PART_BITS);
+}
+
 __device__ __forceinline__ int owner_of(u64 key, int world) {
-    return (int)((mix64(key) >> 40) % (u64)world);
+    return (int)(part_of(key) % (unsigned int)world);
+}
+
+// first slot probed for a key: partition in the top bits, then the top bits of the 64-bit mix
+__device__ __forceinline__ u64 slot_of(const EngineDev &e, u64 key) {
+    return ((u64)part_of(key) << e.slot_bits) | (mix64(key) >> (64 - e.slot_bits));
 }
 
 __device__ __forceinline__ bool better(u64 k1, i64 c1, u64 k2, i64 c2) {
@@ -179,7 +217,7 @@ __device__ __forceinline__ void mark_dirty(const EngineDev &e, u64 slot_index) {
 
 // add delta to key in the pair table, inserting the key when absent
 __device__ __forceinline__ void table_add(const EngineDev &e, u64 key, i64 delta) {
-    u64 h = mix64(key) & e.mask;
+    u64 h = slot_of(e, key);
     for (unsigned int probe = 0; probe < STBPE_MAX_PROBE; ++probe) {
         Slot *s = &e.table[h];
         u64 k = *(volatile u64 *)&s->key;

@@ -33,7 +33,7 @@ struct stbpe_engine {
     bool filter_valid;    // host mirror of DevState::filter_valid
     double filter_density;  // the filter is kept while (matches of the last merge) <= filter_density x tiles
     u64 *dense;           // 65 536 global counters of the byte-level count path
-    unsigned int *big;    // 2^32 directly indexed counters of the 16-bit-vocabulary count path (lazy)
+    PartBuffers parts;    // partition buffers of the 16-bit-vocabulary count path (allocated at first use)
     i64 dense32_min;      // streams shorter than this use the general kernel
     bool only_bytes;      // every token so far came from stbpe_append_bytes (ids < 256)
     ncclComm_t comm;      // own NCCL communicator for the native multi-GPU round loop
@@ -173,7 +173,7 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->comm = nullptr;
     e->all_cands = nullptr;
     e->own_boxes = false;
-    e->big = nullptr;
+    memset(&e->parts, 0, sizeof(e->parts));
     e->dense32_min = 1ll << 24;
     if (const char *v = getenv("STBPE_DENSE32_MIN_TOKENS")) e->dense32_min = atoll(v);
     e->mail_own = nullptr;
@@ -207,9 +207,11 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
         if (slots < (1ull << 20)) slots = 1ull << 20;
         if (slots > cap) slots = cap;
     }
-    slots = next_pow2(slots < (u64)STBPE_BLK ? STBPE_BLK : slots);
+    slots = next_pow2(slots < (u64)2 * STBPE_PARTS ? (u64)2 * STBPE_PARTS : slots);
     e->slots = slots;
     e->d.mask = slots - 1;
+    e->d.slot_bits = 0;
+    while ((1ull << (e->d.slot_bits + STBPE_PART_BITS)) < slots) ++e->d.slot_bits;
     e->d.n_blocks = (unsigned int)(slots / STBPE_BLK);
     e->d.world = cfg->world_size;
     e->d.rank = cfg->rank;
@@ -329,9 +331,17 @@ static int append_common(stbpe_engine *e, const void *data, i64 n, size_t elem, 
     const void *src = data;
     void *staged = nullptr;
     if (!is_device_pointer(data)) {
-        CK(cudaMallocAsync(&staged, (size_t)n * elem, s));
-        CK(cudaMemcpyAsync(staged, data, (size_t)n * elem, cudaMemcpyHostToDevice, s));
-        src = staged;
+        // host data is staged on the device before the pack kernel reads it: in the second stream
+        // buffer when the engine has one (it is idle until the first re-pack, and an allocation of this
+        // size costs as much as the copy), else in stream-ordered scratch
+        if (e->tiles_alt && (size_t)n * elem <= (size_t)e->max_tiles * STBPE_TILE * sizeof(uint32_t)) {
+            src = e->tiles_alt;
+            CK(cudaMemcpyAsync(e->tiles_alt, data, (size_t)n * elem, cudaMemcpyHostToDevice, s));
+        } else {
+            CK(cudaMallocAsync(&staged, (size_t)n * elem, s));
+            CK(cudaMemcpyAsync(staged, data, (size_t)n * elem, cudaMemcpyHostToDevice, s));
+            src = staged;
+        }
     }
     uint32_t *dst = e->d.tiles + e->n_tokens;
     unsigned int *bad = &e->d.st->error;
@@ -488,43 +498,57 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
     }
     if (e->d.n_tiles > 0 && fresh && !mg && !e->only_bytes && e->cfg.base_vocab <= 65536 &&
         e->n_tokens >= e->dense32_min && !getenv("STBPE_NO_DENSE_COUNT")) {
-        // 16-bit vocabulary: directly indexed 32-bit counters in HBM (16 GiB, kept for later counts)
-        const size_t big_bytes = (size_t)4 << 32;
-        if (!e->big) {
+        // 16-bit vocabulary: partition the pairs, then count partition by partition inside L2
+        // (wide_count.cuh).  Buffers are allocated at first use and kept for later counts.
+        PartBuffers &pb = e->parts;
+        // every CTA of the first pass owns a region of every partition: its share of the partition's
+        // words (1 / grid of them, give or take the statistics of its batches) plus head room
+        const int n_cta = e->sm_count;
+        const i64 cap = ((e->max_tokens / STBPE_PARTS / n_cta) * 13 / 10 + 1024 + 3) & ~(i64)3;
+        if (!pb.words) {
             size_t free_b = 0, total_b = 0;
             CK(cudaMemGetInfo(&free_b, &total_b));
-            if (free_b > big_bytes + ((size_t)4 << 30)) {
-                cudaError_t c = dev_alloc(e, &e->big, (size_t)1 << 32);
-                if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc dense pair counters");
-                CK(cudaMemsetAsync(e->big, 0, big_bytes, s));
+            const size_t need = (size_t)STBPE_PARTS * n_cta * cap * sizeof(uint32_t);
+            if (free_b > need + ((size_t)2 << 30)) {
+                cudaError_t c = dev_alloc(e, &pb.words, (size_t)STBPE_PARTS * n_cta * cap);
+                if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc pair partitions");
+                c = dev_alloc(e, &pb.fill, (size_t)STBPE_PARTS * n_cta);
+                if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc partition counters");
+                pb.cap = cap;
+                pb.n_cta = n_cta;
             }
         }
-        if (e->big) {
+        if (pb.words) {
             CK(cudaMemsetAsync(e->dense, 0, 65536 * sizeof(u64), s));
             CK(cudaEventRecord(e->ev0, s));
-            CK(cudaFuncSetAttribute(count_dense32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
-            count_dense32_kernel<<<e->sm_count, STBPE_DENSE_THREADS, 32768 * 4, s>>>(e->d, e->n_tokens, e->dense, e->big);
+            CK(cudaFuncSetAttribute(partition_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    STBPE_PART_SMEM_BYTES));
+            partition_pairs_kernel<<<pb.n_cta, STBPE_PART_THREADS, STBPE_PART_SMEM_BYTES, s>>>(e->d, e->n_tokens,
+                                                                                              e->dense, pb);
             CK(cudaGetLastError());
             CK(cudaEventRecord(e->ev1, s));
             unsigned int derr = 0;
             CK(cudaMemcpyAsync(&derr, &e->d.st->error, sizeof(derr), cudaMemcpyDeviceToHost, s));
             CK(cudaStreamSynchronize(s));
             if (!(derr & STBPE_DERR_DENSE_OVERFLOW)) {
-                CK(cudaEventElapsedTime(&e->count_ms, e->ev0, e->ev1));
+                float pass1 = 0.f;
+                CK(cudaEventElapsedTime(&pass1, e->ev0, e->ev1));
                 CK(cudaEventRecord(e->ev0, s));
                 dense_to_table_kernel<false><<<256, 256, 0, s>>>(e->d, e->dense);
                 CK(cudaGetLastError());
-                dense32_to_table_kernel<<<e->sm_count * 8, 256, 0, s>>>(e->d, e->big);
+                const int per_region = 2;  // blocks per pass-1 region: a region holds some 10^4 words
+                for (int p = 0; p < STBPE_PARTS; ++p)
+                    partition_table_kernel<<<pb.n_cta * per_region, 1024, 0, s>>>(e->d, pb, p, per_region);
                 CK(cudaGetLastError());
                 CK(cudaEventRecord(e->ev1, s));
                 CK(cudaEventSynchronize(e->ev1));
                 CK(cudaEventElapsedTime(&e->convert_ms, e->ev0, e->ev1));
+                e->count_ms = pass1 + e->convert_ms;  // the pair table is complete only after both passes
                 return STBPE_OK;
             }
-            // an id of 65 536 or more: discard what was counted and use the general kernel
+            // an id of 65 536 or more, or a partition outgrew its buffer: discard and use the general kernel
             derr &= ~STBPE_DERR_DENSE_OVERFLOW;
             CK(cudaMemcpyAsync(&e->d.st->error, &derr, sizeof(derr), cudaMemcpyHostToDevice, s));
-            CK(cudaMemsetAsync(e->big, 0, big_bytes, s));
             CK(cudaStreamSynchronize(s));
         }
     }

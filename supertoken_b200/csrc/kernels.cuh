@@ -167,80 +167,11 @@ __global__ void __launch_bounds__(STBPE_DENSE_THREADS, 1)
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// K2, wide dense path: a fresh stream whose ids are all below 65 536 (a 16-bit vocabulary).  The pair
-// space is then 2^32 keys and its histogram fits HBM as a directly indexed array of 2^32 32-bit
-// counters (16 GiB of the 180): a token costs one fire-and-forget 32-bit reduction on
-// (a << 16) | b, with no hashing, no probing and no compare-and-swap.  Pairs whose two ids are
-// below 256 (the most frequent ids of a frequency-ranked vocabulary) take the shared-memory path of
-// the byte-level kernel instead and never reach the memory system.  A 32-bit counter cannot
-// overflow: a stream holds fewer than 2^32 pairs.  An id of 65 536 or more raises
-// STBPE_DERR_DENSE_OVERFLOW and the host recounts with the general kernel.
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void dense32_add(unsigned int *s_tab, u64 *g_dense, unsigned int *big,
-                                            unsigned int *derr, uint32_t t0, uint32_t t1) {
-    if (t1 & STBPE_FLAG) return;  // the right token starts a row (or lies past the end)
-    t0 &= ~STBPE_FLAG;
-    const uint32_t both = t0 | t1;
-    if (both < 256u) {
-        dense_add(s_tab, g_dense, derr, t0, t1);
-    } else if (both < 65536u) {
-        atomicAdd(&big[(t0 << 16) | t1], 1u);  // result unused: a reduction, not a round trip
-    } else {
-        atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
-    }
-}
-
-__global__ void __launch_bounds__(STBPE_DENSE_THREADS, 1)
-    count_dense32_kernel(EngineDev e, i64 n_tokens, u64 *g_dense, unsigned int *big) {
-    extern __shared__ __align__(16) unsigned int s_tab[];  // 32 768 words
-    for (int i = threadIdx.x; i < 32768; i += STBPE_DENSE_THREADS) s_tab[i] = 0u;
-    __syncthreads();
-    const uint32_t *tok = e.tiles;
-    unsigned int *derr = &e.st->error;
-    const int lane = threadIdx.x & 31;
-    const i64 span = (i64)STBPE_DENSE_THREADS * 4;
-    for (i64 base = (i64)blockIdx.x * span * STBPE_DENSE_UNROLL; base < n_tokens;
-         base += (i64)gridDim.x * span * STBPE_DENSE_UNROLL) {
-        uint4 v[STBPE_DENSE_UNROLL];
-        uint32_t nx[STBPE_DENSE_UNROLL];
-#pragma unroll
-        for (int u = 0; u < STBPE_DENSE_UNROLL; ++u) {
-            const i64 i = base + u * span + (i64)threadIdx.x * 4;
-            if (i + 4 <= n_tokens) {
-                v[u] = *reinterpret_cast<const uint4 *>(tok + i);
-            } else {
-                v[u].x = i < n_tokens ? tok[i] : STBPE_NONE;
-                v[u].y = i + 1 < n_tokens ? tok[i + 1] : STBPE_NONE;
-                v[u].z = i + 2 < n_tokens ? tok[i + 2] : STBPE_NONE;
-                v[u].w = i + 3 < n_tokens ? tok[i + 3] : STBPE_NONE;
-            }
-            nx[u] = (lane == 31) ? (i + 4 < n_tokens ? tok[i + 4] : STBPE_NONE) : 0u;
-        }
-#pragma unroll
-        for (int u = 0; u < STBPE_DENSE_UNROLL; ++u) {
-            uint32_t n0 = __shfl_down_sync(0xFFFFFFFFu, v[u].x, 1);
-            if (lane == 31) n0 = nx[u];
-            dense32_add(s_tab, g_dense, big, derr, v[u].x, v[u].y);
-            dense32_add(s_tab, g_dense, big, derr, v[u].y, v[u].z);
-            dense32_add(s_tab, g_dense, big, derr, v[u].z, v[u].w);
-            dense32_add(s_tab, g_dense, big, derr, v[u].w, n0);
-        }
-    }
-    __syncthreads();
-    for (int p = threadIdx.x; p < 32768; p += STBPE_DENSE_THREADS) {
-        const unsigned int x = s_tab[p];
-        const unsigned int w = (unsigned int)p ^ (((unsigned int)p >> 7) & 31u);  // inverse of dense_word
-        if (x & 0xFFFFu) atomicAdd(&g_dense[2 * w], (u64)(x & 0xFFFFu));
-        if (x >> 16) atomicAdd(&g_dense[2 * w + 1], (u64)(x >> 16));
-    }
-}
-
 // Insert a key that is known to be absent (every directly indexed counter is its own key, and the
 // table was cleared before the count): one compare-and-swap claims the slot, the count is a plain
 // store, and nothing is marked dirty because a full refresh follows the initial count.
 __device__ __forceinline__ bool table_insert_unique(const EngineDev &e, u64 key, i64 count) {
-    u64 h = mix64(key) & e.mask;
+    u64 h = slot_of(e, key);
     for (unsigned int probe = 0; probe < STBPE_MAX_PROBE; ++probe) {
         Slot *s = &e.table[h];
         if (atomicCAS(&s->key, STBPE_EMPTY, key) == STBPE_EMPTY) {
@@ -253,27 +184,7 @@ __device__ __forceinline__ bool table_insert_unique(const EngineDev &e, u64 key,
     return false;
 }
 
-// 2^32 directly indexed counters -> entries of the pair table; every counter read is left at zero,
-// so the array is clean for the next count without a 16 GiB memset.
-__global__ void __launch_bounds__(256) dense32_to_table_kernel(EngineDev e, unsigned int *big) {
-    uint4 *v = reinterpret_cast<uint4 *>(big);
-    const u64 n4 = 1ull << 30;
-    unsigned int mine = 0;
-    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (u64)gridDim.x * blockDim.x) {
-        const uint4 c = __ldcs(v + i);  // streamed once
-        if ((c.x | c.y | c.z | c.w) == 0u) continue;
-        const u64 k = i * 4;
-        const u64 a = k >> 16, b = k & 0xFFFFu;
-        if (c.x) mine += table_insert_unique(e, (a << 32) | b, (i64)c.x);
-        if (c.y) mine += table_insert_unique(e, (a << 32) | (b + 1), (i64)c.y);
-        if (c.z) mine += table_insert_unique(e, (a << 32) | (b + 2), (i64)c.z);
-        if (c.w) mine += table_insert_unique(e, (a << 32) | (b + 3), (i64)c.w);
-        v[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) mine += __shfl_down_sync(0xFFFFFFFFu, mine, d);
-    if ((threadIdx.x & 31) == 0 && mine) atomicAdd(&e.st->n_keys, (u64)mine);
-}
+#include "wide_count.cuh"
 
 // dense 16-bit keys -> entries of the pair table (or of the rank-local delta table)
 template <bool MG>
@@ -332,7 +243,7 @@ __global__ void refresh_kernel(EngineDev e, int all) {
 }
 
 __device__ __forceinline__ i64 find_slot(const EngineDev &e, u64 key) {
-    u64 h = mix64(key) & e.mask;
+    u64 h = slot_of(e, key);
     for (unsigned int probe = 0; probe < STBPE_MAX_PROBE; ++probe) {
         const u64 k = *(volatile u64 *)&e.table[h].key;
         if (k == key) return (i64)h;

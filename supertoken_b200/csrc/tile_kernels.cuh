@@ -24,11 +24,15 @@
 #define STBPE_NCW 8                              // consumer warps per CTA
 #endif
 #ifndef STBPE_NS
-#define STBPE_NS 16                              // ring stages per CTA
+#define STBPE_NS 8                               // ring stages per CTA
 #endif
 #ifndef STBPE_MIN_CTAS
-#define STBPE_MIN_CTAS 2                         // resident CTAs per SM the kernels are compiled for
+#define STBPE_MIN_CTAS 3                         // resident CTAs per SM the kernels are compiled for
 #endif
+// Measured on the first 20 merges of a 1 GiB corpus (every tile visited and rewritten): 8 warps x 16
+// stages x 2 CTAs per SM 1.93 TB/s, 8 x 8 x 3 CTAs (24 consumer warps per SM, one stage each)
+// 2.06 TB/s, 16 x 16 x 2 and 12 x 12 x 2 slower (registers spill or fewer CTAs fit), 8 x 24 x 2 far
+// slower (one CTA per SM).
 // STBPE_NS must be a multiple of STBPE_NCW: then a stage is always consumed by the same warp, and
 // a parity wait can never be more than one phase ahead of its barrier (a waiter that is two
 // phases early would see the older phase of equal parity as "complete" and run onto stale data)
@@ -291,53 +295,63 @@ template <bool MG>
 __device__ __forceinline__ void merge_delta_terms(const SmemTable &tab, const EngineDev &e, uint32_t a, uint32_t b,
                                                   uint32_t nw, uint32_t tm2, uint32_t tm1, uint32_t t0, uint32_t t1,
                                                   uint32_t t2, uint32_t t3, int tile_x, int tile_own) {
-    // every pair that comes into being (+1 term) is also entered into the pair filter of the tile
-    // that holds its left token: tile_x for the token before the head, tile_own for the head
+    // Every window yields at most two -1 terms, two +1 terms and two filter entries (every pair that
+    // comes into being is entered into the pair filter of the tile that holds its left token: tile_x
+    // for the token before the head, tile_own for the head).  The terms are worked out first and
+    // added afterwards, so that the lanes of a warp, whose windows fall into different cases, run
+    // through one sequence of adds together instead of one sequence per case.
+    u64 km0 = 0, kp0 = 0, km1 = 0, kp1 = 0;  // keys of the -1 / +1 terms on the left and on the right
+    bool m0 = false, p0 = false, m1 = false, p1 = false, f1 = false;
+    u64 kf1 = 0;
     if (a != b) {
-        if (!(t0 & STBPE_FLAG)) {
+        if (!(t0 & STBPE_FLAG)) {  // x exists
             const bool x_dropped = (tm1 == b) && ((tm2 & STBPE_IDMASK) == a);
-            if (x_dropped) {
-                const u64 k = ((u64)nw << 32) | (u64)nw;
-                smem_table_add<MG>(tab, e, k, 1);
-                filter_set(e, tile_x, k);  // the preceding head became `new` where x's left neighbour was
-            } else {
-                const u64 x = (u64)(tm1 & STBPE_IDMASK) << 32;
-                smem_table_add<MG>(tab, e, x | (u64)a, -1);
-                smem_table_add<MG>(tab, e, x | (u64)nw, 1);
-                filter_set(e, tile_x, x | (u64)nw);
-            }
+            const u64 x = (u64)(tm1 & STBPE_IDMASK) << 32;
+            km0 = x | (u64)a;
+            m0 = !x_dropped;
+            // the preceding head became `new` where x's left neighbour was
+            kp0 = x_dropped ? (((u64)nw << 32) | (u64)nw) : (x | (u64)nw);
+            p0 = true;
         }
-        if (!(t2 & STBPE_FLAG)) {
-            smem_table_add<MG>(tab, e, ((u64)b << 32) | (u64)t2, -1);
-            const bool M2 = (t2 == a) && (t3 == b);
-            const u64 k = ((u64)nw << 32) | (u64)(M2 ? nw : t2);
-            if (!M2) smem_table_add<MG>(tab, e, k, 1);
-            filter_set(e, tile_own, k);
+        if (!(t2 & STBPE_FLAG)) {  // y exists
+            const bool M2 = (t2 == a) && (t3 == b);  // y heads the next match, which adds (new,new) itself
+            km1 = ((u64)b << 32) | (u64)t2;
+            m1 = true;
+            kp1 = ((u64)nw << 32) | (u64)t2;
+            p1 = !M2;
+            kf1 = M2 ? (((u64)nw << 32) | (u64)nw) : kp1;
+            f1 = true;
         }
     } else {
         const bool head = ((t0 & STBPE_IDMASK) == a) && (t1 == b);
         if (head) {
             if (!(t0 & STBPE_FLAG)) {
                 const u64 x = (u64)(tm1 & STBPE_IDMASK) << 32;
-                smem_table_add<MG>(tab, e, x | (u64)a, -1);
-                smem_table_add<MG>(tab, e, x | (u64)nw, 1);
-                filter_set(e, tile_x, x | (u64)nw);
+                km0 = x | (u64)a;
+                kp0 = x | (u64)nw;
+                m0 = p0 = true;
             }
-        } else if (!(t1 & STBPE_FLAG)) {
-            smem_table_add<MG>(tab, e, ((u64)a << 32) | (u64)t1, -1);
-            const u64 k = ((u64)nw << 32) | (u64)t1;
-            smem_table_add<MG>(tab, e, k, 1);
-            filter_set(e, tile_own, k);  // right when the run started in this tile; the tile where a
-                                          // run that crosses tiles started is a wildcard instead
+        } else if (!(t1 & STBPE_FLAG)) {  // tail of the run, y = t1
+            km1 = ((u64)a << 32) | (u64)t1;
+            kp1 = ((u64)nw << 32) | (u64)t1;
+            m1 = p1 = true;
+            kf1 = kp1;  // right when the run started in this tile; the tile where a run that crosses
+            f1 = true;  // tiles started is a wildcard instead
         }
     }
+    if (m0) smem_table_add<MG>(tab, e, km0, -1);
+    if (p0) smem_table_add<MG>(tab, e, kp0, 1);
+    if (m1) smem_table_add<MG>(tab, e, km1, -1);
+    if (p1) smem_table_add<MG>(tab, e, kp1, 1);
+    if (p0) filter_set(e, tile_x, kp0);
+    if (f1) filter_set(e, tile_own, kf1);
 }
 
 // Remove the first live token of a tile that this merge does not otherwise visit: it is the b of
 // a match whose head is the last token of the preceding tile.  One warp shifts the tile left by one
 // token in global memory (chunk by chunk: all reads of a chunk, then its writes) and writes the
 // tile's next record.  Nobody else touches this tile during the merge.
-__device__ __forceinline__ void drop_first_token(const EngineDev &e, int tile, int m, int lane) {
+__device__ __noinline__ void drop_first_token(const EngineDev &e, int tile, int m, int lane) {
     TileRec r;
     const int slot = current_rec(e, tile, m, r);
     uint32_t *g = e.tiles + (i64)tile * STBPE_TILE;

@@ -1,0 +1,230 @@
+// K2, wide path: first count of a fresh stream whose ids are all below 65 536 (a 16-bit vocabulary).
+//
+// The pair space is 2^32 keys and a Zipf-like id stream touches 10^8 of them, so a histogram kept in
+// one place is bound by random memory accesses, not by the stream (one scattered reduction per token
+// into a table in HBM ran at 37 G sector requests per second, 4 % of the stream rate).  Random
+// reductions are six times faster while their target stays in L2 (measured on B200: 227 G per second
+// into 64 MB, 21 G per second into 4 GB), so the count is split in two passes that never touch HBM at
+// random:
+//
+//   pass 1  partition_pairs_kernel reads the stream once.  Pairs of two ids below 256 (44 % of a
+//           Zipf(1.1) stream) go to 16-bit shared-memory counters as in the byte-level kernel.  Every
+//           other pair becomes one 32-bit word, mix32((a << 16) | b), and is appended to the
+//           partition named by the word's top 8 bits: per CTA a ring of 64 words per partition in
+//           shared memory, flushed with coalesced stores after every batch of tokens into a region
+//           of the partition that belongs to this CTA alone (no reservation, hence no atomic and no
+//           round trip to memory in the loop; with one global cursor per partition the flush waited
+//           for 256 dependent reservations per batch and the pass took 13.4 ms instead of 4).  The
+//           mix is a bijection, so partitions are balanced whatever the ids, and the word still
+//           identifies the pair.
+//   pass 2  partition_table_kernel, one launch per partition: every word is turned back into its
+//           pair (unmix32) and added to the pair table.  The slot index of a key starts with the
+//           same 8 partition bits, so all adds of a launch fall into one slice of the table
+//           (1/256 of it: 32 MB of an 8 GiB table), which stays in L2 while the launch runs; the
+//           words are streamed past it with evict-first loads.  (An intermediate block of 2^24
+//           directly indexed 32-bit counters per partition, 64 MB, was tried first: together with
+//           the table slice it did not stay in L2 and the pass ran at the HBM rate, 43.5 ms.)
+//
+// An id of 65 536 or more, or a partition region that outgrows its buffer, raises
+// STBPE_DERR_DENSE_OVERFLOW and the host recounts with the general kernel.
+#pragma once
+#include "common.cuh"
+
+#define STBPE_PART_RING 64          // words per partition and CTA between two flushes
+#define STBPE_PART_THREADS 1024
+#define STBPE_PART_UNROLL 2         // uint4 loads per thread and batch: 8 192 tokens per CTA batch
+#define STBPE_PART_CACHE_BITS 12    // log2 of the entries of the per-CTA word cache of pass 2 (32 KB)
+#define STBPE_PART_CACHE (1 << STBPE_PART_CACHE_BITS)
+#define STBPE_PART_SHIFT (32 - STBPE_PART_BITS)
+#define STBPE_PART_SMEM_BYTES (32768 * 4 + STBPE_PARTS * STBPE_PART_RING * 4 + 2 * STBPE_PARTS * 4)
+
+struct PartBuffers {
+    uint32_t *words;        // [partition][CTA of pass 1] regions of `cap` words
+    unsigned int *fill;     // words in each region
+    i64 cap;
+    int n_cta;              // grid size of pass 1
+};
+
+__device__ __forceinline__ void part_append(const PartBuffers &pb, unsigned int *s_ring, unsigned int *s_cur,
+                                            unsigned int *s_fill, unsigned int *derr, uint32_t word) {
+    const unsigned int p = word >> STBPE_PART_SHIFT;
+    const unsigned int pos = atomicAdd(&s_cur[p], 1u);
+    if (pos < STBPE_PART_RING) {
+        // rings fill at about the same pace, so slot `pos` of every ring would sit in the same bank:
+        // rotate each ring by its partition number
+        s_ring[p * STBPE_PART_RING + ((pos + p) & (STBPE_PART_RING - 1))] = word;
+    } else {  // ring full before the flush (far out in the tail of the batch statistics): append directly
+        const unsigned int g = atomicAdd(&s_fill[p], 1u);
+        if ((i64)g < pb.cap)
+            pb.words[((i64)p * pb.n_cta + blockIdx.x) * pb.cap + g] = word;
+        else
+            atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
+    }
+}
+
+__device__ __forceinline__ void part_pair(const PartBuffers &pb, unsigned int *s_tab, unsigned int *s_ring,
+                                          unsigned int *s_cur, unsigned int *s_fill, u64 *g_dense,
+                                          unsigned int *derr, uint32_t t0, uint32_t t1) {
+    if (t1 & STBPE_FLAG) return;  // the right token starts a row (or lies past the end)
+    t0 &= ~STBPE_FLAG;
+    const uint32_t both = t0 | t1;
+    if (both < 256u)
+        dense_add(s_tab, g_dense, derr, t0, t1);
+    else if (both < 65536u)
+        part_append(pb, s_ring, s_cur, s_fill, derr, mix32((t0 << 16) | t1));
+    else
+        atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
+}
+
+__global__ void __launch_bounds__(STBPE_PART_THREADS, 1)
+    partition_pairs_kernel(EngineDev e, i64 n_tokens, u64 *g_dense, PartBuffers pb) {
+    extern __shared__ __align__(16) unsigned int s_all[];
+    unsigned int *s_tab = s_all;                                  // 32 768 words of 16-bit counters
+    unsigned int *s_ring = s_all + 32768;                         // STBPE_PARTS rings
+    unsigned int *s_cur = s_ring + STBPE_PARTS * STBPE_PART_RING;  // ring fill
+    unsigned int *s_fill = s_cur + STBPE_PARTS;                   // words this CTA has stored per partition
+    for (int i = threadIdx.x; i < 32768; i += STBPE_PART_THREADS) s_tab[i] = 0u;
+    for (int i = threadIdx.x; i < STBPE_PARTS; i += STBPE_PART_THREADS) s_cur[i] = s_fill[i] = 0u;
+    __syncthreads();
+    const uint32_t *tok = e.tiles;
+    unsigned int *derr = &e.st->error;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const i64 span = (i64)STBPE_PART_THREADS * 4;
+    uint4 v[STBPE_PART_UNROLL];
+    uint32_t nx[STBPE_PART_UNROLL];
+    // the loads of a batch are issued before the flush of the batch before it, so that their trip to
+    // memory runs under the flush and its two CTA barriers
+    auto load_batch = [&](i64 base) {
+#pragma unroll
+        for (int u = 0; u < STBPE_PART_UNROLL; ++u) {
+            const i64 i = base + u * span + (i64)threadIdx.x * 4;
+            if (i + 4 <= n_tokens) {
+                v[u] = __ldcs(reinterpret_cast<const uint4 *>(tok + i));
+            } else {
+                v[u].x = i < n_tokens ? tok[i] : STBPE_NONE;
+                v[u].y = i + 1 < n_tokens ? tok[i + 1] : STBPE_NONE;
+                v[u].z = i + 2 < n_tokens ? tok[i + 2] : STBPE_NONE;
+                v[u].w = i + 3 < n_tokens ? tok[i + 3] : STBPE_NONE;
+            }
+            nx[u] = (lane == 31) ? (i + 4 < n_tokens ? tok[i + 4] : STBPE_NONE) : 0u;
+        }
+    };
+    const i64 step = (i64)gridDim.x * span * STBPE_PART_UNROLL;
+    i64 base = (i64)blockIdx.x * span * STBPE_PART_UNROLL;
+    if (base < n_tokens) load_batch(base);
+    for (; base < n_tokens; base += step) {
+#pragma unroll
+        for (int u = 0; u < STBPE_PART_UNROLL; ++u) {
+            uint32_t n0 = __shfl_down_sync(0xFFFFFFFFu, v[u].x, 1);
+            if (lane == 31) n0 = nx[u];
+            part_pair(pb, s_tab, s_ring, s_cur, s_fill, g_dense, derr, v[u].x, v[u].y);
+            part_pair(pb, s_tab, s_ring, s_cur, s_fill, g_dense, derr, v[u].y, v[u].z);
+            part_pair(pb, s_tab, s_ring, s_cur, s_fill, g_dense, derr, v[u].z, v[u].w);
+            part_pair(pb, s_tab, s_ring, s_cur, s_fill, g_dense, derr, v[u].w, n0);
+        }
+        if (base + step < n_tokens) load_batch(base + step);
+        __syncthreads();
+        // flush: one warp per ring, two coalesced stores of 128 bytes at most, into this CTA's region
+        for (int p = warp; p < STBPE_PARTS; p += STBPE_PART_THREADS / 32) {
+            const unsigned int n = min(s_cur[p], (unsigned int)STBPE_PART_RING);
+            if (n == 0u) continue;
+            const unsigned int g = s_fill[p];
+            __syncwarp();
+            if ((i64)g + n <= pb.cap) {
+                uint32_t *dst = pb.words + ((i64)p * pb.n_cta + blockIdx.x) * pb.cap + g;
+                for (unsigned int k = lane; k < n; k += 32)
+                    dst[k] = s_ring[p * STBPE_PART_RING + ((k + p) & (STBPE_PART_RING - 1))];
+            } else if (lane == 0) {
+                atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
+            }
+            if (lane == 0) {
+                s_fill[p] = g + n;
+                s_cur[p] = 0u;
+            }
+        }
+        __syncthreads();
+    }
+    for (int p = threadIdx.x; p < STBPE_PARTS; p += STBPE_PART_THREADS) {
+        const unsigned int n = s_fill[p];
+        pb.fill[(i64)p * pb.n_cta + blockIdx.x] = (i64)n < pb.cap ? n : (unsigned int)pb.cap;
+    }
+    for (int p = threadIdx.x; p < 32768; p += STBPE_PART_THREADS) {
+        const unsigned int x = s_tab[p];
+        const unsigned int w = (unsigned int)p ^ (((unsigned int)p >> 7) & 31u);  // inverse of dense_word
+        if (x & 0xFFFFu) atomicAdd(&g_dense[2 * w], (u64)(x & 0xFFFFu));
+        if (x >> 16) atomicAdd(&g_dense[2 * w + 1], (u64)(x >> 16));
+    }
+}
+
+// Add n occurrences of a key to the pair table during the first count: no maxima to keep (a full
+// refresh follows), and a key that is already there costs one load and one reduction without result.
+__device__ __forceinline__ bool table_count_n(const EngineDev &e, u64 key, u64 h, u64 n, unsigned int &fresh) {
+    for (unsigned int probe = 0; probe < STBPE_MAX_PROBE; ++probe) {
+        Slot *s = &e.table[h];
+        u64 k = __ldcg(&s->key);
+        if (k == STBPE_EMPTY) {
+            const u64 old = atomicCAS(&s->key, STBPE_EMPTY, key);
+            if (old == STBPE_EMPTY) {
+                ++fresh;
+                k = key;
+            } else {
+                k = old;
+            }
+        }
+        if (k == key) {
+            atomicAdd((u64 *)&s->count, n);  // result unused: a reduction
+            return true;
+        }
+        h = (h + 1) & e.mask;
+    }
+    atomicOr(&e.st->error, STBPE_DERR_TABLE_FULL);
+    return false;
+}
+
+__device__ __forceinline__ void part_word_to_table(const EngineDev &e, uint32_t x, u64 n, unsigned int &fresh) {
+    const uint32_t ab = unmix32(x);
+    const u64 key = ((u64)(ab >> 16) << 32) | (u64)(ab & 0xFFFFu);
+    const u64 h = ((u64)(x >> STBPE_PART_SHIFT) << e.slot_bits) | (mix64(key) >> (64 - e.slot_bits));
+    table_count_n(e, key, h, n, fresh);
+}
+
+// pass 2: the words of partition p (the regions of all pass-1 CTAs) into the table slice of p.
+// Block b serves region b / per_region.  A frequent pair would otherwise be tens of thousands of
+// reductions on one address, which L2 executes one after the other (the hottest pair of a partition
+// alone took longer than everything else of its launch), so every block first collects its words in
+// a direct-mapped cache in shared memory (word -> count; a word whose entry is taken by another
+// goes straight to the table) and then adds each cached word once.
+__global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, PartBuffers pb, int p, int per_region) {
+    __shared__ uint32_t s_word[STBPE_PART_CACHE];
+    __shared__ unsigned int s_cnt[STBPE_PART_CACHE];
+    for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
+        s_word[i] = 0xFFFFFFFFu;
+        s_cnt[i] = 0u;
+    }
+    __syncthreads();
+    const int region = blockIdx.x / per_region, part = blockIdx.x % per_region;
+    const i64 n = pb.fill[(i64)p * pb.n_cta + region];
+    const uint32_t *w = pb.words + ((i64)p * pb.n_cta + region) * pb.cap;
+    unsigned int fresh = 0;
+    for (i64 i = (i64)part * blockDim.x + threadIdx.x; i < n; i += (i64)per_region * blockDim.x) {
+        const uint32_t x = __ldcs(w + i);  // streamed once: keep it from displacing the table slice
+        const unsigned int c = (x * 0x9E3779B1u) >> (32 - STBPE_PART_CACHE_BITS);
+        uint32_t k = s_word[c];
+        if (k == 0xFFFFFFFFu && x != 0xFFFFFFFFu) {
+            const uint32_t old = atomicCAS(&s_word[c], 0xFFFFFFFFu, x);
+            k = old == 0xFFFFFFFFu ? x : old;
+        }
+        if (k == x && x != 0xFFFFFFFFu)
+            atomicAdd(&s_cnt[c], 1u);
+        else
+            part_word_to_table(e, x, 1ull, fresh);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
+        const unsigned int c = s_cnt[i];
+        if (c) part_word_to_table(e, s_word[i], (u64)c, fresh);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) fresh += __shfl_down_sync(0xFFFFFFFFu, fresh, d);
+    if ((threadIdx.x & 31) == 0 && fresh) atomicAdd(&e.st->n_keys, (u64)fresh);
+}

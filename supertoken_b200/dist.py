@@ -43,9 +43,31 @@ def mix64(x: int) -> int:
     return x
 
 
+_M32 = (1 << 32) - 1
+
+
+def mix32(x: int) -> int:
+    """The invertible 32-bit mix that names a key's partition (``mix32`` in ``csrc/common.cuh``)."""
+    x &= _M32
+    x ^= x >> 16
+    x = (x * 0x7FEB352D) & _M32
+    x ^= x >> 15
+    x = (x * 0x846CA68B) & _M32
+    x ^= x >> 16
+    return x
+
+
+def part_of(key: int) -> int:
+    """Partition (0..255) of a packed pair key: top bits of its slot in the pair table, partition of
+    the first count of a 16-bit vocabulary, and - modulo the number of ranks - its owner."""
+    a, b = (key >> 32) & _M32, key & _M32
+    folded = ((a << 16) ^ b ^ ((a >> 16) * 0x9E3779B1) ^ ((b >> 16) * 0x85EBCA77)) & _M32
+    return mix32(folded) >> 24
+
+
 def owner_of(key: int, world: int) -> int:
     """Rank that owns a packed pair key (``owner_of`` in ``csrc/common.cuh``)."""
-    return (mix64(key) >> 40) % world
+    return part_of(key) % world
 
 
 def shard_rows(row_offsets: np.ndarray, world: int) -> List[Tuple[int, int]]:

@@ -7,7 +7,9 @@ import torch
 
 from supertoken_b200 import synth
 from supertoken_b200.bpe_trainer import GPUBPETrainer, _flatten_batch, hash_merge_pair
-from supertoken_b200.export import build_artifacts, bytes_to_unicode, write_artifacts
+from supertoken_b200.export import (build_artifacts, bytes_to_unicode, load_tiktoken_merges,
+                                    load_warm_start_merges, write_artifacts)
+from tests.helpers import load_golden
 
 
 def test_generators_numpy_equals_torch():
@@ -83,11 +85,118 @@ def test_cli_parses_the_reference_flags(tmp_path):
     args = cli.build_parser().parse_args(
         ["train-bpe", "--data", str(tmp_path / "*.txt"), "--bos", "1", "--eos", "2", "--seed", "3", "--device", "cuda",
          "--merges", "10", "--base-vocab", "256", "--target-util", "0.5", "--min-batch", "1", "--max-batch", "8",
-         "--token-bytes", "1024", "--log-every", "5", "--out-dir", str(tmp_path / "o"), "--privacy", "--privacy-salt", "s",
+         "--token-bytes", "1024", "--log-every", "5", "--out-dir", str(tmp_path / "o"), "--privacy", "tie-randomize", "--privacy-salt", "s",
          "--tie-seed", "4", "--checkpoint-dir", str(tmp_path / "c"), "--checkpoint-every", "5", "--dry-run",
-         "--warm-start", "3", "--io-workers", "2", "--prefetch-batches", "2", "--prefetch-jitter", "0.1", "--code-mode",
+         "--warm-start", "seeds.json", "--io-workers", "2", "--prefetch-batches", "2", "--prefetch-jitter", "0.1", "--code-mode",
          "--meta-compress", "--aug-strength", "0.2"])
-    assert args.merges == 10 and args.privacy and args.dry_run
+    assert args.merges == 10 and args.privacy == "tie-randomize" and args.dry_run and args.warm_start == "seeds.json"
     assert cli.main(["train-bpe", "--data", str(tmp_path / "*.txt"), "--dry-run"]) == 0
     data, off = cli.load_rows([str(tmp_path / "a.txt")], 300, None)
     assert data.dtype == np.int32 and data[0] == 300 and off.tolist() == [0, 12]
+
+
+def test_artifact_files_equal_the_reference_writers_byte_for_byte(tmp_path):
+    # tests/golden/extra.json holds the five files GPUBPETrainer.save_artifacts of the reference wrote
+    for case in load_golden("extra.json")["artifacts"]:
+        merges = [tuple(m) for m in case["merges"]]
+        t = GPUBPETrainer(base_vocab=case["base_vocab"], merges=len(merges), device="cuda:0")
+        t.merges, t.vocab_size = merges, case["base_vocab"] + len(merges)
+        paths = t.save_artifacts(tmp_path / f"a{case['base_vocab']}")
+        for key, p in paths.items():
+            name = p.split("/")[-1]
+            got = open(p, "rb").read().decode("utf-8")
+            if key == "metadata":
+                meta = json.loads(got)
+                meta.pop("tiktoken_merges_path")
+                got = json.dumps(meta, sort_keys=True)
+            assert got == case["files"][name], name
+        # and the way back: the merges can be read from the files as the reference's loaders read them
+        assert load_tiktoken_merges(paths["tiktoken_merges"], base_vocab=case["base_vocab"]) == merges or case["base_vocab"] != 256
+        assert load_warm_start_merges(paths["metadata"]) == merges
+    tok = t.export_tokenizer(tmp_path / "tok")
+    assert tok.vocab and tok.artifact_path.endswith("tokenizer.json")
+
+
+def test_checkpoints_written_by_the_reference_load(tmp_path):
+    g = load_golden("extra.json")
+    ck = g["checkpoint"]
+    t = GPUBPETrainer(merges=ck["target"], device="cuda:0")
+    rec = t.load_state_dict({"payload": ck["state_json"], "tensors": {}})
+    assert [list(m) for m in t.merges] == ck["merges_at_checkpoint"] and t.vocab_size == 256 + len(t.merges)
+    assert rec["step"] == len(t.merges) and rec["sequences"] is not None
+    # the rows in the checkpoint are the input rows with the checkpoint's merges applied
+    from oracle import oracle as O
+    ids, off = O.flatten_rows(ck["rows"])
+    for i, (a, b) in enumerate(t.merges):
+        O.apply_merge_flat(ids, off, a, b, 256 + i)
+    assert [r for r in rec["sequences"]] == [ids[off[i]:off[i + 1]].tolist() for i in range(len(off) - 1)]
+    # a checkpoint of a run with randomised ties carries the generator's state
+    tie = g["ties"][1]
+    t = GPUBPETrainer(merges=tie["target"], device="cuda:0")
+    rec = t.load_state_dict({"payload": tie["checkpoint_after_6"]})
+    assert t.randomize_ties and t._tie_seed_value == 123 and rec["sequences"] is None
+    import random
+    fresh = random.Random(123)
+    assert t._tie_rng.getstate() != fresh.getstate()
+    # our own checkpoint files have the reference's layout and round-trip
+    t.save_checkpoint(tmp_path / "ck", include_batches=False)
+    state = t.load_checkpoint(tmp_path / "ck")
+    assert set(state) == {"payload", "tensors"} and set(state["payload"]) >= {"version", "trainer", "dataset", "rng"}
+    assert set(state["tensors"]) == {"cached_pair_keys", "cached_pair_counts"}
+    t2 = GPUBPETrainer(merges=3, device="cuda:0")
+    t2.load_state_dict(state)
+    assert t2.merges == t.merges and t2._tie_rng.getstate() == t._tie_rng.getstate()
+    assert state["payload"]["trainer"]["model"]["merges"] == tie["checkpoint_after_6"]["trainer"]["model"]["merges"]
+
+
+REFERENCE = "/root/reference"
+
+
+@pytest.mark.skipif(not __import__("os").path.isdir(REFERENCE), reason="needs the reference checkout")
+def test_drop_in_seam_of_the_reference_command_line(tmp_path, monkeypatch):
+    """The swap a maintainer makes: rebind ``GPUBPETrainer`` in the reference's modules, then use the
+    reference's own ``train-bpe`` parser and trainer factory (``main.py:21-30``, ``:661-689``, ``:2180-2363``).
+    Runs where the reference source tree exists; constructing the trainer needs no GPU."""
+    import importlib
+    import inspect
+    import sys
+    monkeypatch.syspath_prepend(REFERENCE)
+    monkeypatch.chdir(tmp_path)
+    ref_mod = importlib.import_module("gpu_tokenizer.bpe_trainer")
+    ref_cls = ref_mod.GPUBPETrainer
+    import supertoken_b200.base as base_mod
+    importlib.reload(base_mod)   # picks the reference's BaseTrainer now that it is importable
+    import supertoken_b200.bpe_trainer as ours_mod
+    importlib.reload(ours_mod)
+    ours = ours_mod.GPUBPETrainer
+    try:
+        from gpu_tokenizer.trainers.base import BaseTrainer
+        assert issubclass(ours, BaseTrainer)
+        for name in ("__init__", "fit"):
+            assert list(inspect.signature(getattr(ours, name)).parameters) == \
+                list(inspect.signature(getattr(ref_cls, name)).parameters), name
+        for name in ("state_dict", "save_checkpoint"):
+            assert set(inspect.signature(getattr(ref_cls, name)).parameters) <= \
+                set(inspect.signature(getattr(ours, name)).parameters), name
+        for attr in ("merges", "vocab_size", "base_vocab", "target_merges", "devices", "device", "autoscaler",
+                     "sync_every", "metrics", "throughput_metrics", "handle_chunk_start", "import_merges",
+                     "precompute_warm_start_plan", "state_dict", "load_state_dict", "save_checkpoint",
+                     "load_checkpoint", "export_tokenizer", "save_artifacts", "save", "_bytes_to_unicode",
+                     "_enable_histogram_cache", "_top_pairs_limit", "_cpu_fallback_batches", "_active_batch_size"):
+            assert hasattr(ours(merges=1, device="cuda:0"), attr), attr
+        main = importlib.import_module("main")
+        monkeypatch.setattr(ref_mod, "GPUBPETrainer", ours)
+        monkeypatch.setattr(main, "GPUBPETrainer", ours)
+        (tmp_path / "a.txt").write_bytes(b"hello hello world")
+        args = main._parser().parse_args(
+            ["train-bpe", "--data", str(tmp_path / "a.txt"), "--merges", "12", "--base-vocab", "256", "--device", "cuda:0",
+             "--out-dir", str(tmp_path / "out"), "--log-every", "0", "--tie-seed", "3", "--checkpoint-every", "4",
+             "--checkpoint-dir", str(tmp_path / "ck"), "--io-workers", "1", "--target-util", "0.8"])
+        assert args.func is main._cmd_train_bpe
+        trainer = main._build_bpe_trainer(args)[0]    # the reference's own factory (main.py:661-689)
+        assert isinstance(trainer, ours) and trainer.target_merges == 12 and trainer.base_vocab == 256
+    finally:
+        for m in [k for k in sys.modules if k == "main" or k.startswith("gpu_tokenizer")]:
+            sys.modules.pop(m, None)
+        importlib.reload(base_mod)
+        importlib.reload(ours_mod)

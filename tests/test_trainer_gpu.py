@@ -101,7 +101,7 @@ def test_fit_bytes_and_artifacts(tmp_path):
     # checkpoint round trip + warm start from the checkpointed merges reproduces the run
     t.save_checkpoint(tmp_path / "ck")
     t2 = GPUBPETrainer(merges=64, device="cuda:0")
-    t2.load_checkpoint(tmp_path / "ck")
+    t2.load_state_dict(t2.load_checkpoint(tmp_path / "ck"))
     assert t2.merges == om
     t3 = GPUBPETrainer(merges=64, device="cuda:0", warm_start_merges=om[:20])
     assert t3.fit_bytes(c.data, c.row_offsets)["merges"] == om
@@ -118,9 +118,26 @@ def test_resume_equals_uninterrupted_run_and_warm_start_plan(tmp_path):
     half.save_checkpoint(tmp_path / "ck")
     resumed = GPUBPETrainer(merges=50, device="cuda")
     state = json.load(open(tmp_path / "ck" / "state.json"))
-    state["trainer"]["target_merges"] = 50
-    resumed.fit(batches, log_every=0, resume_state=state)
+    assert state["dataset"]["batches"]["sequences"]            # the rewritten rows are in the checkpoint
+    state["trainer"]["model"]["target_merges"] = 50
+    resumed.fit([], log_every=0, resume_state=state)           # continues from those rows: no batches needed
     assert resumed.merges == full.merges and resumed.vocab_size == full.vocab_size
+    assert resumed.merge_counts == full.merge_counts[20:]
+    # a checkpoint without rows: the merges are replayed on the batches
+    half.save_checkpoint(tmp_path / "ck2", include_batches=False)
+    state = half.load_checkpoint(tmp_path / "ck2")
+    assert "batches" not in state["payload"]["dataset"] and state["tensors"]["cached_pair_keys"].numel() > 0
+    state["payload"]["trainer"]["model"]["target_merges"] = 50
+    replayed = GPUBPETrainer(merges=50, device="cuda")
+    replayed.fit(batches, log_every=0, resume_state=state)
+    assert replayed.merges == full.merges
+    # the histogram in tensors.pt is the histogram after the checkpoint's merges
+    ids, off = O.flatten_rows(rows)
+    for i, (a, b) in enumerate(half.merges):
+        O.apply_merge_flat(ids, off, a, b, 256 + i)
+    k, cnt = O.count_pairs_flat(ids[:off[-1]].copy(), off, 1)
+    assert state["tensors"]["cached_pair_keys"].numpy().astype(np.uint64).tolist() == k.tolist()
+    assert state["tensors"]["cached_pair_counts"].tolist() == cnt.tolist()
     # warm-start plan = the top-k bigrams of the initial histogram (ties to the smaller key)
     ids, off = O.flatten_rows(rows)
     k, cnt = O.count_pairs_flat(ids, off, 1)
@@ -146,3 +163,41 @@ def test_cli_train_bpe(tmp_path):
     assert [tuple(m) for m in meta["merges"]] == om
     assert open(out / "merges.txt", encoding="utf-8").read().splitlines()[0] == "#version: 0.2"
     assert cli.main(["train-bpe", "--data", str(tmp_path / "nothing*"), "--out-dir", str(out)]) == 2
+
+
+def test_randomised_ties_follow_the_reference_over_many_tied_merges(tmp_path):
+    # tests/golden/extra.json: runs of the reference with randomize_ties=True on rows where every
+    # selection is a tie between several pairs, so each merge is the seeded generator's pick
+    g = load_golden("extra.json")
+    for case in g["ties"]:
+        t = GPUBPETrainer(base_vocab=case["base_vocab"], merges=case["target"], device="cuda",
+                          randomize_ties=True, tie_seed=case["tie_seed"])
+        t.fit([make_batch(case["rows"])], log_every=0)
+        assert [list(m) for m in t.merges] == case["merges"]
+        plain = GPUBPETrainer(base_vocab=case["base_vocab"], merges=case["target"], device="cuda")
+        plain.fit([make_batch(case["rows"])], log_every=0)
+        assert [list(m) for m in plain.merges] == case["merges_without_randomisation"]
+    # interrupted and resumed: a checkpoint written by the reference after 6 of 12 merges, and one
+    # written here, both continue to the merges of the uninterrupted reference run
+    case = g["ties"][1]
+    t = GPUBPETrainer(base_vocab=256, merges=case["target"], device="cuda")
+    payload = json.loads(json.dumps(case["checkpoint_after_6"]))
+    payload["trainer"]["model"]["target_merges"] = case["target"]
+    t.fit([make_batch(case["rows"])], log_every=0, resume_state={"payload": payload})
+    assert [list(m) for m in t.merges] == case["merges"]
+    t = GPUBPETrainer(base_vocab=256, merges=case["target"], device="cuda", randomize_ties=True, tie_seed=case["tie_seed"])
+    t.fit([make_batch(case["rows"])], log_every=0, checkpoint_interval=5, checkpoint_dir=str(tmp_path / "ck"))
+    state = t.load_checkpoint(tmp_path / "ck")               # written after merge 10 of 12
+    assert len(state["payload"]["trainer"]["model"]["merges"]) == 10 and "tie_breaker" in state["payload"]["rng"]
+    t2 = GPUBPETrainer(base_vocab=256, merges=case["target"], device="cuda")
+    t2.fit([], log_every=0, resume_state=state)
+    assert [list(m) for m in t2.merges] == case["merges"]
+
+
+def test_checkpoint_written_by_the_reference_resumes_here():
+    ck = load_golden("extra.json")["checkpoint"]
+    t = GPUBPETrainer(base_vocab=ck["base_vocab"], merges=ck["target"], device="cuda")
+    payload = json.loads(json.dumps(ck["state_json"]))
+    payload["trainer"]["model"]["target_merges"] = ck["target"]
+    t.fit([], log_every=0, resume_state={"payload": payload, "tensors": {}})
+    assert [list(m) for m in t.merges] == ck["merges_final"]
