@@ -252,6 +252,10 @@ def run_reference_arm(args, wl):
 
 # ----------------------------------------------------------------------------- count-only workload
 def run_count_bench(args, wl, dev):
+    print(json.dumps(count_bench(wl, dev, args.steps, max(args.warmup, 1))), flush=True)
+
+
+def count_bench(wl, dev, K, W, with_e2e=True):
     """Initial pair-count microbenchmark on an id stream (16-bit vocabulary): every step loads the
     resident ids again (pack, untimed) and runs one full histogram pass.  `value` is GB/s at 4 bytes
     per token over the device time of all kernels of the count, from the first read of the stream
@@ -260,7 +264,6 @@ def run_count_bench(args, wl, dev):
     from supertoken_b200 import synth
     from supertoken_b200.engine import Engine
     gen, n_tokens, seed, _, desc = wl
-    K, W = args.steps, max(args.warmup, 1)
     ids, off = synth.config3_ids(n_tokens, seed=seed, device=str(dev))
     torch.cuda.synchronize()
     off_np = off.cpu().numpy()
@@ -289,19 +292,23 @@ def run_count_bench(args, wl, dev):
     med = float(np.median(ms))
     gbs = 4.0 * n_tokens / (med / 1e3) / 1e9
     # end to end: pinned host ids -> device -> pack -> histogram -> best pair back on the host
-    host = torch.empty(n_tokens, dtype=torch.int32, pin_memory=True)
-    host.copy_(ids)
-    del ids
-    torch.cuda.empty_cache()
-    torch.cuda.synchronize()
-    t = time.perf_counter()
-    eng.reset()
-    eng.append_ids(host, off_np)
-    eng.count_initial()
-    k2, c2, _ = eng.select_best(False)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t
-    assert (k2, c2) == (key, count)
+    e2e_s = None
+    if with_e2e:
+        host = torch.empty(n_tokens, dtype=torch.int32, pin_memory=True)
+        host.copy_(ids)
+        del ids
+        torch.cuda.empty_cache()
+        torch.cuda.synchronize()
+        t = time.perf_counter()
+        eng.reset()
+        eng.append_ids(host, off_np)
+        eng.count_initial()
+        k2, c2, _ = eng.select_best(False)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t
+        assert (k2, c2) == (key, count)
+        del host
+    eng.close()
     line = {
         "metric": "pair_count_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": med, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -315,11 +322,12 @@ def run_count_bench(args, wl, dev):
                      "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak,
                      "frac_of_8tbs": gbs / 8000.0, "kernel_ms": med, "second_pass_ms": float(np.median(conv)),
                      "call_ms": float(np.median(call)), "traffic": None},
-        "e2e": {"value": 4.0 * n_tokens / e2e_s / 1e9, "unit": "GB/s", "seconds": e2e_s,
-                "h2d_bytes_per_step": 4.0 * n_tokens + off_np.nbytes, "d2h_bytes_per_step": 24.0},
-        "gpu_launches": 2 * K, "clocks": clocks, "cpu_baseline": None,
+        "e2e": None if e2e_s is None else {"value": 4.0 * n_tokens / e2e_s / 1e9, "unit": "GB/s", "seconds": e2e_s,
+                                           "h2d_bytes_per_step": 4.0 * n_tokens + off_np.nbytes,
+                                           "d2h_bytes_per_step": 24.0},
+        "gpu_launches": 258 * K, "clocks": clocks, "cpu_baseline": None,   # first pass, hot pairs, one launch per partition
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -332,6 +340,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--bytes", type=int, default=None, help="override the corpus size (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-c3", action="store_true", help="skip the config-3 pair-count block of the default run")
     args = ap.parse_args()
     wl = list(WORKLOADS[args.workload])
     if args.bytes:
@@ -467,6 +476,19 @@ def main():
                              f"{scale:.4f} to the full corpus (recount cost is linear in tokens)"}
         del ids, off
 
+    # the initial pair count BASELINE.json names as its microbenchmark (config 3: 2^31 ids over a
+    # 65 536 vocabulary), two passes beside the merge job so that it reaches the same record
+    pair_count_c3 = None
+    if args.workload == "c2" and not args.bytes and not args.no_c3:
+        del host
+        torch.cuda.empty_cache()
+        c3 = count_bench(list(WORKLOADS["c3"]), dev, 2, 1, with_e2e=False)
+        pair_count_c3 = {"workload": c3["config"]["workload"], "gbs": c3["value"], "ms": c3["ms_per_step"],
+                         "second_pass_ms": c3["roofline"]["second_pass_ms"], "kernel": c3["roofline"]["kernel"],
+                         "frac_of_measured_peak": c3["roofline"]["frac"], "frac_of_8tbs": c3["roofline"]["frac_of_8tbs"],
+                         "distinct_pairs": c3["config"]["distinct_pairs"], "best_pair": c3["config"]["best_pair"],
+                         "bytes_per_token": 4}
+
     line = {
         "metric": "bpe_merges_per_sec", "value": value, "unit": "merges/s", "n_gpus": 1, "steps": done,
         "warmup": W, "ms_per_step": loop_ms / done, "higher_is_better": True, "scaling": "strong",
@@ -480,6 +502,7 @@ def main():
                        "frac_of_measured_peak": 4.0 * n_tokens / (count_ms / 1e3) / 1e9 / peak,
                        "frac_of_8tbs": 4.0 * n_tokens / (count_ms / 1e3) / 1e9 / 8000.0,
                        "bytes_per_token": 4, "distinct_pairs": None},
+        "pair_count_c3": pair_count_c3,
         "roofline": {"bound": "hbm", "kernel": "merge_kernel", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "algorithmic_bytes": algo_bytes, "kernel_ms": mrg_ms, "launches": done,
@@ -491,7 +514,7 @@ def main():
         "e2e": {"value": e2e, "unit": "merges/s", "seconds": e2e_s,
                 "h2d_bytes_per_step": (n_tokens + off_np.nbytes) / max(len(learned), 1),
                 "d2h_bytes_per_step": 24.0},
-        "gpu_launches": 4 * done + 1,
+        "gpu_launches": 2 * done + 2,   # decide_kernel + merge_kernel per merge, count and the final decision
         "clocks": clocks,
         "cpu_baseline": cpu,
     }

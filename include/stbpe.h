@@ -216,6 +216,33 @@ int stbpe_mg_peer_close(stbpe_engine *e);
 int stbpe_mg_peer_mailbox(stbpe_engine *e, void **out);
 int stbpe_mg_peer_set(stbpe_engine *e, const void *const *mailboxes, int32_t n);
 
+/* First count of an id stream over a vocabulary of at most 65 536 ids on several ranks of one NVLink
+ * domain.  Replaces, for this case, the count + cross-rank reduce of the reference's first loop
+ * iteration (gpu_tokenizer/utils.py:558-635 followed by :863-978, which gathers every rank's whole
+ * key list): every rank partitions the pairs of its own rows, and the rank that owns a partition
+ * (partition modulo world_size, the same rule that owns the keys during the merge loop) counts it out
+ * of all ranks' buffers with peer loads.
+ *   stbpe_mg_wide_export : allocates this rank's partition buffers and returns their 64-byte CUDA IPC
+ *                          handle; the caller gathers the handles of all ranks
+ *   stbpe_mg_wide_open   : maps the buffers of the other ranks (world x 64 bytes, indexed by rank)
+ *   stbpe_mg_wide_block / stbpe_mg_wide_set : the same for ranks of one process, as device pointers
+ *   stbpe_mg_wide_pass1  : partitions this rank's rows; *ok = 0 if the stream does not qualify (bytes,
+ *                          an id of 65 536 or more, a full buffer).  Synchronises the stream.
+ *   -- the caller synchronises the ranks here (any barrier) and checks that every rank reported ok;
+ *      if one did not, all skip the second pass and the ordinary count round does the counting --
+ *   stbpe_mg_wide_pass2  : counts the partitions this rank owns.  The next count round
+ *                          (stbpe_mg_count_local, or round 0 of stbpe_mg_run / stbpe_mg_peer_run) then
+ *                          finds the table filled and only exchanges, refreshes and selects.
+ *   stbpe_mg_wide_close  : unmaps the peers' buffers; call on every rank and synchronise the ranks
+ *                          before any of them destroys its engine. */
+int stbpe_mg_wide_export(stbpe_engine *e, void *handle_out64);
+int stbpe_mg_wide_open(stbpe_engine *e, const void *handles, int32_t n_handles);
+int stbpe_mg_wide_block(stbpe_engine *e, void **out);
+int stbpe_mg_wide_set(stbpe_engine *e, const void *const *blocks, int32_t n);
+int stbpe_mg_wide_pass1(stbpe_engine *e, int32_t *ok, void *stream);
+int stbpe_mg_wide_pass2(stbpe_engine *e, void *stream);
+int stbpe_mg_wide_close(stbpe_engine *e);
+
 /* Stateless operators on padded [B, L] batches resident on the device, with the
  * reference's operator signatures.
  * stbpe_rows_count_pairs  <- utils.count_pairs (gpu_tokenizer/utils.py:691-706): unique

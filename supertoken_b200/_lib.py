@@ -69,6 +69,13 @@ SIGNATURES = {
     "stbpe_mg_peer_close": (_int, [_vp]),
     "stbpe_mg_peer_mailbox": (_int, [_vp, _vp]),
     "stbpe_mg_peer_set": (_int, [_vp, _vp, _i32]),
+    "stbpe_mg_wide_export": (_int, [_vp, _vp]),
+    "stbpe_mg_wide_open": (_int, [_vp, _vp, _i32]),
+    "stbpe_mg_wide_block": (_int, [_vp, _vp]),
+    "stbpe_mg_wide_set": (_int, [_vp, _vp, _i32]),
+    "stbpe_mg_wide_pass1": (_int, [_vp, _P(_i32), _vp]),
+    "stbpe_mg_wide_pass2": (_int, [_vp, _vp]),
+    "stbpe_mg_wide_close": (_int, [_vp]),
     "stbpe_rows_count_pairs": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
     "stbpe_rows_count_pairs_noalloc": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp,
                                               ctypes.c_char_p, ctypes.c_size_t]),

@@ -507,6 +507,13 @@ class GPUBPETrainer(BaseTrainer):
             driver = os.environ.get("STBPE_MG_DRIVER", "peer" if same_node and world <= 16 else "nccl")
             loop = D.PeerLoop(e, self.exchange_entries) if driver == "peer" else D.NativeLoop(e, self.exchange_entries)
             closer = getattr(loop, "close", None)
+            if not as_bytes and self.base_vocab <= 65536 and same_node:
+                # a large id stream over a 16-bit vocabulary: the ranks partition their pairs and the
+                # owners count them over peer memory before the first round (supertoken_b200/dist.py)
+                total = torch.tensor([float(goff[-1])], dtype=torch.float64, device=e.device)
+                dist.all_reduce(total)
+                if total.item() >= float(1 << 24):
+                    D.wide_count(e)
         try:
             timings["pair_count"].record(time.perf_counter() - t)
             t = time.perf_counter()
@@ -517,6 +524,8 @@ class GPUBPETrainer(BaseTrainer):
             self.merge_counts = [int(c) for c in counts]
             self.vocab_size = self.base_vocab + len(self.merges)
             st = engines[0].state()
+            if mode == "ranks":
+                D.wide_close(engines[0])
             if closer is not None:
                 closer()
         finally:

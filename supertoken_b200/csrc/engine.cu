@@ -34,6 +34,12 @@ struct stbpe_engine {
     double filter_density;  // the filter is kept while (matches of the last merge) <= filter_density x tiles
     u64 *dense;           // 65 536 global counters of the byte-level count path
     PartBuffers parts;    // partition buffers of the 16-bit-vocabulary count path (allocated at first use)
+    unsigned char *wide_block;             // their allocation: header, fills, hot counters, regions
+    u64 *wide_dense;                       // the hot counters inside it
+    void *wide_mapped[STBPE_MAX_PEERS];    // peers' allocations as mapped into this process
+    WidePeers wide_peers;
+    bool wide_open, wide_counted;          // peers mapped / the table holds a count made by stbpe_mg_wide_pass2
+    bool full_refresh_pending;             // that count marked no block dirty: the next refresh recomputes all maxima
     i64 dense32_min;      // streams shorter than this use the general kernel
     bool only_bytes;      // every token so far came from stbpe_append_bytes (ids < 256)
     ncclComm_t comm;      // own NCCL communicator for the native multi-GPU round loop
@@ -127,6 +133,11 @@ STBPE_VISIBLE int stbpe_destroy(stbpe_engine *e) {
             cudaIpcCloseMemHandle(m);
             m = nullptr;
         }
+    for (void *&m : e->wide_mapped)
+        if (m) {
+            cudaIpcCloseMemHandle(m);
+            m = nullptr;
+        }
     // the NCCL communicator is shared by the engines of this process and lives until exit
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
@@ -147,6 +158,7 @@ static int reset_state(stbpe_engine *e, cudaStream_t s) {
     e->counted = false;
     e->only_bytes = true;
     e->filter_valid = false;
+    e->wide_counted = e->full_refresh_pending = false;
     return STBPE_OK;
 }
 
@@ -174,6 +186,11 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     e->all_cands = nullptr;
     e->own_boxes = false;
     memset(&e->parts, 0, sizeof(e->parts));
+    e->wide_block = nullptr;
+    e->wide_dense = nullptr;
+    memset(e->wide_mapped, 0, sizeof(e->wide_mapped));
+    memset(&e->wide_peers, 0, sizeof(e->wide_peers));
+    e->wide_open = e->wide_counted = e->full_refresh_pending = false;
     e->dense32_min = 1ll << 24;
     if (const char *v = getenv("STBPE_DENSE32_MIN_TOKENS")) e->dense32_min = atoll(v);
     e->mail_own = nullptr;
@@ -452,8 +469,34 @@ static int rebuild_presence(stbpe_engine *e, cudaStream_t s) {
     return STBPE_OK;
 }
 
-static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
-    const bool fresh = e->recs_stale;
+// Buffers of the partitioned first count (wide_count.cuh), one allocation: every CTA of the first
+// pass owns a region of every partition, sized for its share of the partition's words (1 / grid of
+// them, give or take the statistics of its batches) plus head room.
+static int wide_alloc(stbpe_engine *e) {
+    if (e->wide_block) return STBPE_OK;
+    const int n_cta = e->sm_count;
+    const i64 cap = ((e->max_tokens / STBPE_PARTS / n_cta) * 13 / 10 + 1024 + 3) & ~(i64)3;
+    const size_t bytes = STBPE_WIDE_HEADER_BYTES + wide_fill_bytes(n_cta) + 65536 * sizeof(u64) +
+                         (size_t)STBPE_PARTS * n_cta * cap * sizeof(uint32_t);
+    size_t free_b = 0, total_b = 0;
+    CK(cudaMemGetInfo(&free_b, &total_b));
+    if (free_b < bytes + ((size_t)2 << 30)) return fail(e, STBPE_E_CAPACITY, "CUDA out of memory (pair partitions)");
+    cudaError_t c = dev_alloc(e, &e->wide_block, bytes);
+    if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc pair partitions");
+    WideHeader hd;
+    hd.cap = cap;
+    hd.n_cta = n_cta;
+    CK(cudaMemcpy(e->wide_block, &hd, sizeof(hd), cudaMemcpyHostToDevice));
+    e->parts.fill = const_cast<unsigned int *>(wide_fill(e->wide_block));
+    e->wide_dense = const_cast<u64 *>(wide_dense(e->wide_block, n_cta));
+    e->parts.words = const_cast<uint32_t *>(wide_words(e->wide_block, n_cta));
+    e->parts.cap = cap;
+    e->parts.n_cta = n_cta;
+    return STBPE_OK;
+}
+
+// what every count starts with: tile records of a fresh stream, an empty table, no maxima
+static int count_prologue(stbpe_engine *e, cudaStream_t s) {
     e->convert_ms = 0.f;
     int rc = prepare_stream_state(e, s);
     if (rc != STBPE_OK) return rc;
@@ -470,6 +513,46 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
         CK(cudaEventCreate(&e->ev0));
         CK(cudaEventCreate(&e->ev1));
     }
+    return STBPE_OK;
+}
+
+static bool wide_eligible(const stbpe_engine *e, bool fresh) {
+    return e->d.n_tiles > 0 && fresh && !e->only_bytes && e->cfg.base_vocab <= 65536 &&
+           e->n_tokens >= e->dense32_min && !getenv("STBPE_NO_DENSE_COUNT");
+}
+
+// first pass of the partitioned count; *ok = 0 when an id of 65 536 or more or a full region made it give up
+static int wide_pass1(stbpe_engine *e, int *ok, cudaStream_t s) {
+    PartBuffers &pb = e->parts;
+    *ok = 0;
+    CK(cudaMemsetAsync(e->wide_dense, 0, 65536 * sizeof(u64), s));
+    CK(cudaEventRecord(e->ev0, s));
+    CK(cudaFuncSetAttribute(partition_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, STBPE_PART_SMEM_BYTES));
+    partition_pairs_kernel<<<pb.n_cta, STBPE_PART_THREADS, STBPE_PART_SMEM_BYTES, s>>>(e->d, e->n_tokens, e->wide_dense, pb);
+    CK(cudaGetLastError());
+    CK(cudaEventRecord(e->ev1, s));
+    unsigned int derr = 0;
+    CK(cudaMemcpyAsync(&derr, &e->d.st->error, sizeof(derr), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    CK(cudaEventElapsedTime(&e->count_ms, e->ev0, e->ev1));
+    if (derr & STBPE_DERR_DENSE_OVERFLOW) {
+        derr &= ~STBPE_DERR_DENSE_OVERFLOW;
+        CK(cudaMemcpyAsync(&e->d.st->error, &derr, sizeof(derr), cudaMemcpyHostToDevice, s));
+        CK(cudaStreamSynchronize(s));
+        return STBPE_OK;
+    }
+    *ok = 1;
+    return STBPE_OK;
+}
+
+static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
+    if (mg && e->wide_counted) {  // stbpe_mg_wide_pass2 has filled the table already
+        e->wide_counted = false;
+        return STBPE_OK;
+    }
+    const bool fresh = e->recs_stale;
+    int rc = count_prologue(e, s);
+    if (rc != STBPE_OK) return rc;
     if (e->d.n_tiles > 0 && fresh && e->only_bytes && !getenv("STBPE_NO_DENSE_COUNT")) {
         // byte-level fast path: dense stream, ids < 256
         CK(cudaMemsetAsync(e->dense, 0, 65536 * sizeof(u64), s));
@@ -496,61 +579,31 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
         CK(cudaMemcpyAsync(&e->d.st->error, &derr, sizeof(derr), cudaMemcpyHostToDevice, s));
         CK(cudaStreamSynchronize(s));
     }
-    if (e->d.n_tiles > 0 && fresh && !mg && !e->only_bytes && e->cfg.base_vocab <= 65536 &&
-        e->n_tokens >= e->dense32_min && !getenv("STBPE_NO_DENSE_COUNT")) {
+    if (!mg && wide_eligible(e, fresh)) {
         // 16-bit vocabulary: partition the pairs, then count partition by partition inside L2
-        // (wide_count.cuh).  Buffers are allocated at first use and kept for later counts.
-        PartBuffers &pb = e->parts;
-        // every CTA of the first pass owns a region of every partition: its share of the partition's
-        // words (1 / grid of them, give or take the statistics of its batches) plus head room
-        const int n_cta = e->sm_count;
-        const i64 cap = ((e->max_tokens / STBPE_PARTS / n_cta) * 13 / 10 + 1024 + 3) & ~(i64)3;
-        if (!pb.words) {
-            size_t free_b = 0, total_b = 0;
-            CK(cudaMemGetInfo(&free_b, &total_b));
-            const size_t need = (size_t)STBPE_PARTS * n_cta * cap * sizeof(uint32_t);
-            if (free_b > need + ((size_t)2 << 30)) {
-                cudaError_t c = dev_alloc(e, &pb.words, (size_t)STBPE_PARTS * n_cta * cap);
-                if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc pair partitions");
-                c = dev_alloc(e, &pb.fill, (size_t)STBPE_PARTS * n_cta);
-                if (c != cudaSuccess) return cuda_fail(e, c, "cudaMalloc partition counters");
-                pb.cap = cap;
-                pb.n_cta = n_cta;
-            }
+        // (wide_count.cuh).  Buffers are allocated at first use and kept for later counts; without
+        // room for them the general kernel counts.
+        int ok = 0;
+        if (wide_alloc(e) == STBPE_OK) {
+            rc = wide_pass1(e, &ok, s);
+            if (rc != STBPE_OK) return rc;
         }
-        if (pb.words) {
-            CK(cudaMemsetAsync(e->dense, 0, 65536 * sizeof(u64), s));
+        if (ok) {
+            PartBuffers &pb = e->parts;
             CK(cudaEventRecord(e->ev0, s));
-            CK(cudaFuncSetAttribute(partition_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    STBPE_PART_SMEM_BYTES));
-            partition_pairs_kernel<<<pb.n_cta, STBPE_PART_THREADS, STBPE_PART_SMEM_BYTES, s>>>(e->d, e->n_tokens,
-                                                                                              e->dense, pb);
+            dense_to_table_kernel<false><<<256, 256, 0, s>>>(e->d, e->wide_dense);
+            CK(cudaGetLastError());
+            const int per_region = 2;  // blocks per pass-1 region: a region holds some 10^4 words
+            for (int p = 0; p < STBPE_PARTS; ++p)
+                partition_table_kernel<<<pb.n_cta * per_region, 1024, 0, s>>>(e->d, pb, p, per_region);
             CK(cudaGetLastError());
             CK(cudaEventRecord(e->ev1, s));
-            unsigned int derr = 0;
-            CK(cudaMemcpyAsync(&derr, &e->d.st->error, sizeof(derr), cudaMemcpyDeviceToHost, s));
-            CK(cudaStreamSynchronize(s));
-            if (!(derr & STBPE_DERR_DENSE_OVERFLOW)) {
-                float pass1 = 0.f;
-                CK(cudaEventElapsedTime(&pass1, e->ev0, e->ev1));
-                CK(cudaEventRecord(e->ev0, s));
-                dense_to_table_kernel<false><<<256, 256, 0, s>>>(e->d, e->dense);
-                CK(cudaGetLastError());
-                const int per_region = 2;  // blocks per pass-1 region: a region holds some 10^4 words
-                for (int p = 0; p < STBPE_PARTS; ++p)
-                    partition_table_kernel<<<pb.n_cta * per_region, 1024, 0, s>>>(e->d, pb, p, per_region);
-                CK(cudaGetLastError());
-                CK(cudaEventRecord(e->ev1, s));
-                CK(cudaEventSynchronize(e->ev1));
-                CK(cudaEventElapsedTime(&e->convert_ms, e->ev0, e->ev1));
-                e->count_ms = pass1 + e->convert_ms;  // the pair table is complete only after both passes
-                return STBPE_OK;
-            }
-            // an id of 65 536 or more, or a partition outgrew its buffer: discard and use the general kernel
-            derr &= ~STBPE_DERR_DENSE_OVERFLOW;
-            CK(cudaMemcpyAsync(&e->d.st->error, &derr, sizeof(derr), cudaMemcpyHostToDevice, s));
-            CK(cudaStreamSynchronize(s));
+            CK(cudaEventSynchronize(e->ev1));
+            CK(cudaEventElapsedTime(&e->convert_ms, e->ev0, e->ev1));
+            e->count_ms += e->convert_ms;  // the pair table is complete only after both passes
+            return STBPE_OK;
         }
+        // an id of 65 536 or more, or a region outgrew its buffer: the general kernel counts
     }
     if (e->d.n_tiles > 0) {
         int grid = e->count_grid < e->d.n_tiles ? e->count_grid : e->d.n_tiles;
@@ -615,13 +668,20 @@ STBPE_VISIBLE int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *cou
 
 static int filter_policy(stbpe_engine *e, const DevState &h, bool layout_changed, cudaStream_t s);
 
-static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s) {
+// The one CTA that ends decide_kernel can also build the worklist, which saves a launch, but it
+// walks the filter rows alone: measured on 2^20 tiles, 200-400 us per merge instead of 9 us for the
+// 32-CTA worklist_kernel.  Only streams of a few thousand tiles take that route.
+static bool worklist_in_decide(const stbpe_engine *e) { return (e->d.n_tiles + 31) / 32 <= 256; }
+
+static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s, bool have_worklist = false) {
     if (e->d.n_tiles > 0) {
-        const int wl_words = (e->d.n_tiles + 31) / 32;
-        int wl_grid = (wl_words + 1023) / 1024;
-        if (wl_grid > 32) wl_grid = 32;
-        worklist_kernel<<<wl_grid, 1024, 0, s>>>(e->d);
-        CK(cudaGetLastError());
+        if (!have_worklist) {
+            const int wl_words = (e->d.n_tiles + 31) / 32;
+            int wl_grid = (wl_words + 1023) / 1024;
+            if (wl_grid > 32) wl_grid = 32;
+            worklist_kernel<<<wl_grid, 1024, 0, s>>>(e->d);
+            CK(cudaGetLastError());
+        }
         int grid = e->merge_grid < e->d.n_tiles ? e->merge_grid : e->d.n_tiles;
         if (mg)
             merge_kernel<true><<<grid, STBPE_CTA_THREADS, e->merge_smem, s>>>(e->d, e->merge_slots);
@@ -745,12 +805,19 @@ __global__ void set_target_kernel(EngineDev e, int target) {
     e.st->n_matches = 0;
 }
 
+// one iteration of the single-GPU loop: two launches (three when the worklist is too long for one CTA)
 static int enqueue_iteration(stbpe_engine *e, cudaStream_t s) {
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
+    const bool wl = worklist_in_decide(e);
+    decide_kernel<<<e->refresh_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, wl ? 1 : 0);
     CK(cudaGetLastError());
-    int rc = launch_merge(e, false, s);
-    if (rc != STBPE_OK) return rc;
-    return launch_refresh(e, 0, s);
+    return launch_merge(e, false, s, wl);
+}
+
+// the step that ends a batch of iterations: maxima of the last merge's blocks, next selection or stop rule
+static int enqueue_final_decide(stbpe_engine *e, cudaStream_t s) {
+    decide_kernel<<<e->refresh_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 0);
+    CK(cudaGetLastError());
+    return STBPE_OK;
 }
 
 STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
@@ -822,9 +889,12 @@ STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
             if (h.stopped) break;
         }
     }
-    // one more selection decides the stop reason without applying anything when the target is reached
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
-    CK(cudaGetLastError());
+    // one more decision refreshes the maxima of the last merge and gives the stop reason without
+    // applying anything when the target is reached
+    {
+        int rc = enqueue_final_decide(e, s);
+        if (rc != STBPE_OK) return rc;
+    }
     CK(cudaStreamSynchronize(s));
     return check_device_error(e, s);
 }
@@ -870,14 +940,14 @@ STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *ke
         }
         const int step = (e->filter_valid || e->d.n_tiles < 64) ? P : 32;
         n = todo - base < step ? todo - base : step;
+        const bool wl = worklist_in_decide(e);
         for (int i = 0; i < n && rc == STBPE_OK; ++i) {
             cudaEventRecord(ev[4 * i], s);
-            select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
+            decide_kernel<<<e->refresh_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, wl ? 1 : 0);
             cudaEventRecord(ev[4 * i + 1], s);
-            rc = launch_merge(e, false, s);
+            rc = launch_merge(e, false, s, wl);
             cudaEventRecord(ev[4 * i + 2], s);
-            if (rc == STBPE_OK) rc = launch_refresh(e, 0, s);
-            cudaEventRecord(ev[4 * i + 3], s);
+            cudaEventRecord(ev[4 * i + 3], s);  // the refresh is part of the next decide_kernel
         }
         cudaStreamSynchronize(s);
         for (int i = 0; i < n && rc == STBPE_OK; ++i)
@@ -891,8 +961,8 @@ STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *ke
     cudaEventDestroy(r0);
     cudaEventDestroy(r1);
     if (rc != STBPE_OK) return rc;
-    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
-    CK(cudaGetLastError());
+    rc = enqueue_final_decide(e, s);
+    if (rc != STBPE_OK) return rc;
     CK(cudaStreamSynchronize(s));
     return check_device_error(e, s);
 }
@@ -1074,7 +1144,9 @@ STBPE_VISIBLE int stbpe_mg_apply_inbox(stbpe_engine *e, void *stream) {
     if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
     apply_inbox_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
-    return launch_refresh(e, 0, s);
+    const int all = e->full_refresh_pending ? 1 : 0;
+    e->full_refresh_pending = false;
+    return launch_refresh(e, all, s);
 }
 
 STBPE_VISIBLE int stbpe_mg_candidate(stbpe_engine *e, void *cand_dev, void *stream) {
@@ -1095,6 +1167,132 @@ STBPE_VISIBLE int stbpe_mg_commit(stbpe_engine *e, const void *all_cands_dev, vo
     return STBPE_OK;
 }
 
+
+// ------------------------------------------------------------------ first count of a 16-bit vocabulary, several ranks
+// Every rank partitions the pairs of its own rows (first pass); after a barrier that the caller
+// provides, the owner of a partition counts it out of every rank's regions over NVLink peer memory
+// (second pass).  The next count round (stbpe_mg_count_local, or round 0 of stbpe_mg_peer_run /
+// stbpe_mg_run) then finds the table filled and only exchanges, refreshes and selects.
+STBPE_VISIBLE int stbpe_mg_wide_export(stbpe_engine *e, void *handle_out64) {
+    if (!e || !handle_out64) return STBPE_E_BADARG;
+    if (e->cfg.world_size < 2) return fail(e, STBPE_E_STATE, "engine was created with world_size 1");
+    if (e->cfg.world_size > STBPE_MAX_PEERS) return fail(e, STBPE_E_BADARG, "at most 16 ranks share buffers");
+    if (e->cfg.base_vocab > 65536) return fail(e, STBPE_E_STATE, "the partitioned count needs a vocabulary of at most 65 536 ids");
+    CK(cudaSetDevice(e->cfg.device));
+    int rc = wide_alloc(e);
+    if (rc != STBPE_OK) return rc;
+    cudaIpcMemHandle_t h;
+    CK(cudaIpcGetMemHandle(&h, e->wide_block));
+    memcpy(handle_out64, &h, sizeof(h));
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_wide_open(stbpe_engine *e, const void *handles, int32_t n_handles) {
+    if (!e || !handles) return STBPE_E_BADARG;
+    if (!e->wide_block) return fail(e, STBPE_E_STATE, "call stbpe_mg_wide_export first");
+    if (n_handles != e->cfg.world_size) return fail(e, STBPE_E_BADARG, "one handle per rank is needed");
+    if (e->wide_open) return STBPE_OK;
+    CK(cudaSetDevice(e->cfg.device));
+    e->wide_peers.world = e->cfg.world_size;
+    e->wide_peers.rank = e->cfg.rank;
+    for (int r = 0; r < n_handles; ++r) {
+        if (r == e->cfg.rank) {
+            e->wide_peers.block[r] = e->wide_block;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)r * sizeof(h), sizeof(h));
+        void *p = nullptr;
+        CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        e->wide_mapped[r] = p;
+        e->wide_peers.block[r] = (const unsigned char *)p;
+    }
+    e->wide_open = true;
+    return STBPE_OK;
+}
+
+// ranks of one process: the allocations are handed over as plain device pointers
+STBPE_VISIBLE int stbpe_mg_wide_block(stbpe_engine *e, void **out) {
+    if (!e || !out) return STBPE_E_BADARG;
+    if (!e->wide_block) return fail(e, STBPE_E_STATE, "call stbpe_mg_wide_export first");
+    *out = e->wide_block;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_wide_set(stbpe_engine *e, const void *const *blocks, int32_t n) {
+    if (!e || !blocks) return STBPE_E_BADARG;
+    if (!e->wide_block) return fail(e, STBPE_E_STATE, "call stbpe_mg_wide_export first");
+    if (n != e->cfg.world_size) return fail(e, STBPE_E_BADARG, "one block per rank is needed");
+    e->wide_peers.world = e->cfg.world_size;
+    e->wide_peers.rank = e->cfg.rank;
+    for (int r = 0; r < n; ++r) {
+        if (r != e->cfg.rank && !blocks[r]) return fail(e, STBPE_E_BADARG, "null block");
+        e->wide_peers.block[r] = r == e->cfg.rank ? e->wide_block : (const unsigned char *)blocks[r];
+    }
+    e->wide_open = true;
+    return STBPE_OK;
+}
+
+STBPE_VISIBLE int stbpe_mg_wide_pass1(stbpe_engine *e, int32_t *ok, void *stream) {
+    if (!e || !ok) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    *ok = 0;
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->wide_open) return fail(e, STBPE_E_STATE, "call stbpe_mg_wide_open first");
+    const bool fresh = e->recs_stale;
+    int rc = count_prologue(e, s);
+    if (rc != STBPE_OK) return rc;
+    if (e->only_bytes || e->d.n_tiles < 1 || !fresh) {
+        // nothing to partition here (no rows on this rank, or bytes): an empty first pass, the peers still read it
+        CK(cudaMemsetAsync(e->parts.fill, 0, wide_fill_bytes(e->parts.n_cta), s));
+        CK(cudaMemsetAsync(e->wide_dense, 0, 65536 * sizeof(u64), s));
+        CK(cudaStreamSynchronize(s));
+        *ok = e->d.n_tiles < 1 ? 1 : 0;
+        return STBPE_OK;
+    }
+    int good = 0;
+    rc = wide_pass1(e, &good, s);
+    *ok = good;
+    return rc;
+}
+
+STBPE_VISIBLE int stbpe_mg_wide_pass2(stbpe_engine *e, void *stream) {
+    if (!e) return STBPE_E_BADARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    CK(cudaSetDevice(e->cfg.device));
+    if (!e->wide_open) return fail(e, STBPE_E_STATE, "call stbpe_mg_wide_open first");
+    const int world = e->cfg.world_size, n_cta = e->parts.n_cta;
+    CK(cudaEventRecord(e->ev0, s));
+    dense_peers_to_table_kernel<<<256, 256, 0, s>>>(e->d, e->wide_peers, n_cta);
+    CK(cudaGetLastError());
+    for (int p = e->cfg.rank; p < STBPE_PARTS; p += world)
+        partition_table_peers_kernel<<<n_cta * 2, 1024, 0, s>>>(e->d, e->wide_peers, p, n_cta);
+    CK(cudaGetLastError());
+    CK(cudaEventRecord(e->ev1, s));
+    CK(cudaEventSynchronize(e->ev1));
+    CK(cudaEventElapsedTime(&e->convert_ms, e->ev0, e->ev1));
+    e->count_ms += e->convert_ms;
+    e->wide_counted = true;
+    e->full_refresh_pending = true;
+    e->counted = true;
+    return check_device_error(e, s);
+}
+
+// Unmap the peers' buffers (call on every rank, then synchronise the ranks, before any destroys its engine).
+STBPE_VISIBLE int stbpe_mg_wide_close(stbpe_engine *e) {
+    if (!e) return STBPE_E_BADARG;
+    CK(cudaSetDevice(e->cfg.device));
+    CK(cudaDeviceSynchronize());
+    for (int r = 0; r < STBPE_MAX_PEERS; ++r) {
+        if (e->wide_mapped[r]) {
+            CK(cudaIpcCloseMemHandle(e->wide_mapped[r]));
+            e->wide_mapped[r] = nullptr;
+        }
+        if (r != e->cfg.rank) e->wide_peers.block[r] = nullptr;
+    }
+    e->wide_open = false;
+    return STBPE_OK;
+}
 
 // ------------------------------------------------------------------ rounds over peer memory
 // The exchange of a round done by the kernels themselves: every rank owns a mailbox that its peers
@@ -1195,7 +1393,9 @@ static int enqueue_peer_round(stbpe_engine *e, bool count_round, cudaStream_t s)
     CK(cudaGetLastError());
     apply_peer_kernel<<<e->sm_count * 4, 256, 0, s>>>(e->d);
     CK(cudaGetLastError());
-    rc = launch_refresh(e, 0, s);
+    const int all = e->full_refresh_pending ? 1 : 0;
+    e->full_refresh_pending = false;
+    rc = launch_refresh(e, all, s);
     if (rc != STBPE_OK) return rc;
     select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 3, 0, e->cand, e->cfg.max_merges);
     CK(cudaGetLastError());

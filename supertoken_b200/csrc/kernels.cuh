@@ -198,11 +198,10 @@ __global__ void dense_to_table_kernel(EngineDev e, const u64 *g_dense) {
 // ---------------------------------------------------------------------------------------
 // K4  arg-max: block maxima refresh + reduction with the reference's tie-break
 // ---------------------------------------------------------------------------------------
-__global__ void refresh_kernel(EngineDev e, int all) {
-    const unsigned int n = all ? e.n_blocks : min(e.st->n_dirty, e.n_blocks);
+// recompute the maximum of blocks [w0, n) of the dirty list (or of all blocks), one warp per block
+__device__ __forceinline__ void refresh_blocks(const EngineDev &e, int all, unsigned int n, unsigned int w,
+                                               unsigned int nwarps) {
     const unsigned int lane = threadIdx.x & 31;
-    unsigned int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const unsigned int nwarps = (gridDim.x * blockDim.x) >> 5;
     for (; w < n; w += nwarps) {
         const unsigned int blk = all ? w : e.dirty_list[w];
         const Slot *base = e.table + (u64)blk * STBPE_BLK;
@@ -240,6 +239,11 @@ __global__ void refresh_kernel(EngineDev e, int all) {
                 e.dirty2_list[atomicAdd(&e.st->n_dirty2, 1u)] = sb;
         }
     }
+}
+
+__global__ void refresh_kernel(EngineDev e, int all) {
+    const unsigned int n = all ? e.n_blocks : min(e.st->n_dirty, e.n_blocks);
+    refresh_blocks(e, all, n, (blockIdx.x * blockDim.x + threadIdx.x) >> 5, (gridDim.x * blockDim.x) >> 5);
 }
 
 __device__ __forceinline__ i64 find_slot(const EngineDev &e, u64 key) {
@@ -331,6 +335,47 @@ __device__ __forceinline__ void block_best(u64 &bk, i64 &bc, u64 *s_k, i64 *s_c)
 
 #include "peer_kernels.cuh"
 
+// recompute the maximum of super-blocks [w, n) of the second dirty list (or of all): one warp per
+// super-block, 256 block maxima, 8 per lane
+__device__ __forceinline__ void refresh_super_blocks(const EngineDev &e, int all2, unsigned int n2, unsigned int w,
+                                                     unsigned int nwarps) {
+    const unsigned int lane = threadIdx.x & 31;
+    for (unsigned int i = w; i < n2; i += nwarps) {
+        const unsigned int sb = all2 ? i : e.dirty2_list[i];
+        u64 bk = STBPE_EMPTY;
+        i64 bc = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const unsigned int blk = sb * 256u + j * 32u + lane;
+            if (blk < e.n_blocks) {
+                const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(e.blockmax + blk));
+                const u64 k = ((u64)raw.y << 32) | raw.x;
+                const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
+                if (c > 0 && better(k, c, bk, bc)) {
+                    bk = k;
+                    bc = c;
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const u64 ok = __shfl_down_sync(0xFFFFFFFFu, bk, d);
+            const i64 oc = __shfl_down_sync(0xFFFFFFFFu, bc, d);
+            if (better(ok, oc, bk, bc)) {
+                bk = ok;
+                bc = oc;
+            }
+        }
+        if (lane == 0) {
+            Slot s;
+            s.key = bk;
+            s.count = bc;
+            e.supermax[sb] = s;
+            e.dirty2_flag[sb] = 0u;
+        }
+    }
+}
+
 // mode 0: peek (result into the state); 1: single rank, advance or stop; 2: candidate of this rank
 // into cand; 3: candidate of this rank into every peer mailbox, then wait for the peers' candidates
 // and commit (target = the merge target of the engine)
@@ -342,44 +387,8 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
     __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
     __shared__ int s_last;
     const unsigned int n2 = all2 ? e.n_super2 : min(st->n_dirty2, e.n_super2);
-    {   // one warp per super-block: 256 block maxima, 8 per lane
-        const unsigned int lane = threadIdx.x & 31;
-        const unsigned int wpb = STBPE_SELECT_THREADS / 32;
-        for (unsigned int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < n2; i += gridDim.x * wpb) {
-            const unsigned int sb = all2 ? i : e.dirty2_list[i];
-            u64 bk = STBPE_EMPTY;
-            i64 bc = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const unsigned int blk = sb * 256u + j * 32u + lane;
-                if (blk < e.n_blocks) {
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(e.blockmax + blk);
-                    const u64 k = ((u64)raw.y << 32) | raw.x;
-                    const i64 c = (i64)(((u64)raw.w << 32) | raw.z);
-                    if (c > 0 && better(k, c, bk, bc)) {
-                        bk = k;
-                        bc = c;
-                    }
-                }
-            }
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) {
-                const u64 ok = __shfl_down_sync(0xFFFFFFFFu, bk, d);
-                const i64 oc = __shfl_down_sync(0xFFFFFFFFu, bc, d);
-                if (better(ok, oc, bk, bc)) {
-                    bk = ok;
-                    bc = oc;
-                }
-            }
-            if (lane == 0) {
-                Slot s;
-                s.key = bk;
-                s.count = bc;
-                e.supermax[sb] = s;
-                e.dirty2_flag[sb] = 0u;
-            }
-        }
-    }
+    refresh_super_blocks(e, all2, n2, blockIdx.x * (STBPE_SELECT_THREADS / 32) + (threadIdx.x >> 5),
+                         gridDim.x * (STBPE_SELECT_THREADS / 32));
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -428,13 +437,10 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
 // A partner in a tile that is not visited is dropped by the warp that owns the head (fix-up in the
 // merge kernel).  This kernel builds the bitmap of visited tiles and the compact worklist.
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
+// the tiles merge (cur_a, cur_b) must visit: bitmap and compact list; `block` of `n_blocks` thread
+// blocks of blockDim.x threads share the words of the bitmap
+__device__ __forceinline__ void build_worklist(const EngineDev &e, int block, int n_blocks) {
     DevState *st = e.st;
-    if (st->stopped || st->exchange_only) return;
-    if (!st->filter_valid) {  // stale filter: the merge visits every tile
-        if (blockIdx.x == 0 && threadIdx.x == 0) st->n_work = -1;
-        return;
-    }
     unsigned int r1, r2, r3;
     filter_rows(((u64)(uint32_t)st->cur_a << 32) | (u64)(uint32_t)st->cur_b, r1, r2, r3);
     const unsigned int *row1 = e.presence + (size_t)r1 * e.presence_words;
@@ -443,11 +449,11 @@ __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
     const unsigned int *wild = e.presence + (size_t)STBPE_PROWS * e.presence_words;
     const int n_words = (e.n_tiles + 31) / 32;
     const int lane = threadIdx.x & 31;
-    for (int w0 = blockIdx.x * blockDim.x; w0 < n_words; w0 += gridDim.x * blockDim.x) {
+    for (int w0 = block * blockDim.x; w0 < n_words; w0 += n_blocks * blockDim.x) {
         const int w = w0 + threadIdx.x;
         unsigned int c = 0;
         if (w < n_words) {
-            c = (row1[w] & row2[w] & row3[w]) | wild[w];
+            c = (__ldcg(row1 + w) & __ldcg(row2 + w) & __ldcg(row3 + w)) | __ldcg(wild + w);
             const int rem = e.n_tiles - w * 32;
             if (rem < 32) c &= (1u << rem) - 1u;
             e.cand_bits[w] = c;
@@ -470,6 +476,64 @@ __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
             e.worklist[base++] = (unsigned int)(w * 32 + bit);
         }
     }
+}
+
+__global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
+    DevState *st = e.st;
+    if (st->stopped || st->exchange_only) return;
+    if (!st->filter_valid) {  // stale filter: the merge visits every tile
+        if (blockIdx.x == 0 && threadIdx.x == 0) st->n_work = -1;
+        return;
+    }
+    build_worklist(e, blockIdx.x, gridDim.x);
+}
+
+// The single-GPU loop's step between two merges in one launch: block maxima of the blocks the last
+// merge touched (all CTAs), then, in the CTA that finishes last, the super-block maxima, the
+// arg-max, the bookkeeping of the selected merge (or a stop rule) and, with `with_worklist`, the
+// tiles it has to visit (short streams only: one CTA walks the filter rows far slower than the
+// 32-CTA worklist_kernel).  As separate launches refresh and select took 9 + 14 us of a 70 us merge
+// late in a run, most of it launch latency and dependent round trips to memory.
+__global__ void __launch_bounds__(STBPE_SELECT_THREADS) decide_kernel(EngineDev e, int with_worklist) {
+    DevState *st = e.st;
+    if (st->stopped) return;
+    __shared__ u64 s_k[STBPE_SELECT_THREADS / 32];
+    __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
+    __shared__ int s_last;
+    refresh_blocks(e, 0, min(st->n_dirty, e.n_blocks), (blockIdx.x * blockDim.x + threadIdx.x) >> 5,
+                   (gridDim.x * blockDim.x) >> 5);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = (atomicAdd(&st->ticket, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    refresh_super_blocks(e, 0, min(*(volatile unsigned int *)&st->n_dirty2, e.n_super2), threadIdx.x >> 5,
+                         STBPE_SELECT_THREADS / 32);
+    __syncthreads();
+    u64 bk = STBPE_EMPTY;
+    i64 bc = 0;
+    for (unsigned int i = threadIdx.x; i < e.n_super2; i += STBPE_SELECT_THREADS) {
+        const volatile Slot *p = e.supermax + i;
+        const u64 k = p->key;
+        const i64 c = p->count;
+        if (c > 0 && better(k, c, bk, bc)) {
+            bk = k;
+            bc = c;
+        }
+    }
+    block_best(bk, bc, s_k, s_c);
+    if (threadIdx.x == 0) {
+        st->ticket = 0;
+        st->n_dirty2 = 0;
+        advance_or_stop(e, bk, bc);
+        if (!st->stopped && !st->filter_valid) st->n_work = -1;  // stale filter: every tile
+        __threadfence();
+    }
+    __syncthreads();
+    if (with_worklist && !*(volatile int *)&st->stopped && *(volatile int *)&st->filter_valid) build_worklist(e, 0, 1);
 }
 
 // (Re)build the pair filter from the stream: after a load and after every re-pack.  One CTA handles

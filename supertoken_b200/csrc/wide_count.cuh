@@ -32,7 +32,8 @@
 
 #define STBPE_PART_RING 64          // words per partition and CTA between two flushes
 #define STBPE_PART_THREADS 1024
-#define STBPE_PART_UNROLL 2         // uint4 loads per thread and batch: 8 192 tokens per CTA batch
+#define STBPE_PART_UNROLL 3         // uint4 loads per thread and batch: 12 288 tokens per CTA batch
+static_assert(STBPE_PARTS == 8 * (STBPE_PART_THREADS / 32), "a warp of the first pass serves eight rings");
 #define STBPE_PART_CACHE_BITS 12    // log2 of the entries of the per-CTA word cache of pass 2 (32 KB)
 #define STBPE_PART_CACHE (1 << STBPE_PART_CACHE_BITS)
 #define STBPE_PART_SHIFT (32 - STBPE_PART_BITS)
@@ -44,6 +45,34 @@ struct PartBuffers {
     i64 cap;
     int n_cta;              // grid size of pass 1
 };
+
+// Several ranks: every rank partitions its own rows, then the owner of a partition (partition modulo
+// the number of ranks) counts the partition's words out of every rank's regions with plain peer
+// loads over NVLink, and sums the ranks' counters of the hot pairs it owns.  The buffers of a rank
+// live in one allocation that its peers map: a header {cap, n_cta}, the region fills, the 65 536 hot
+// counters, the regions.
+#define STBPE_WIDE_HEADER_BYTES 256
+struct WideHeader {
+    i64 cap;
+    int n_cta;
+};
+struct WidePeers {
+    const unsigned char *block[STBPE_MAX_PEERS];  // every rank's allocation ([rank] = own)
+    int world, rank;
+};
+__host__ __device__ __forceinline__ size_t wide_fill_bytes(int n_cta) {
+    return (((size_t)STBPE_PARTS * n_cta * sizeof(unsigned int)) + 255) & ~(size_t)255;
+}
+__host__ __device__ __forceinline__ const unsigned int *wide_fill(const unsigned char *block) {
+    return reinterpret_cast<const unsigned int *>(block + STBPE_WIDE_HEADER_BYTES);
+}
+__host__ __device__ __forceinline__ const u64 *wide_dense(const unsigned char *block, int n_cta) {
+    return reinterpret_cast<const u64 *>(block + STBPE_WIDE_HEADER_BYTES + wide_fill_bytes(n_cta));
+}
+__host__ __device__ __forceinline__ const uint32_t *wide_words(const unsigned char *block, int n_cta) {
+    return reinterpret_cast<const uint32_t *>(block + STBPE_WIDE_HEADER_BYTES + wide_fill_bytes(n_cta) +
+                                              65536 * sizeof(u64));
+}
 
 __device__ __forceinline__ void part_append(const PartBuffers &pb, unsigned int *s_ring, unsigned int *s_cur,
                                             unsigned int *s_fill, unsigned int *derr, uint32_t word) {
@@ -65,15 +94,15 @@ __device__ __forceinline__ void part_append(const PartBuffers &pb, unsigned int 
 __device__ __forceinline__ void part_pair(const PartBuffers &pb, unsigned int *s_tab, unsigned int *s_ring,
                                           unsigned int *s_cur, unsigned int *s_fill, u64 *g_dense,
                                           unsigned int *derr, uint32_t t0, uint32_t t1) {
-    if (t1 & STBPE_FLAG) return;  // the right token starts a row (or lies past the end)
+    // the classes are worked out first and the two kinds of add follow one another, so that the lanes
+    // of a warp, whose pairs fall into different classes, share the instructions of each kind
     t0 &= ~STBPE_FLAG;
-    const uint32_t both = t0 | t1;
-    if (both < 256u)
-        dense_add(s_tab, g_dense, derr, t0, t1);
-    else if (both < 65536u)
-        part_append(pb, s_ring, s_cur, s_fill, derr, mix32((t0 << 16) | t1));
-    else
-        atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
+    const uint32_t both = t0 | t1;             // bit 31 set: the right token starts a row or lies past the end
+    const bool hot = both < 256u;
+    const bool wide = !hot && both < 65536u;
+    if (hot) dense_add(s_tab, g_dense, derr, t0, t1);
+    if (wide) part_append(pb, s_ring, s_cur, s_fill, derr, mix32((t0 << 16) | t1));
+    if (!hot && !wide && !(t1 & STBPE_FLAG)) atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
 }
 
 __global__ void __launch_bounds__(STBPE_PART_THREADS, 1)
@@ -124,20 +153,22 @@ __global__ void __launch_bounds__(STBPE_PART_THREADS, 1)
         }
         if (base + step < n_tokens) load_batch(base + step);
         __syncthreads();
-        // flush: one warp per ring, two coalesced stores of 128 bytes at most, into this CTA's region
-        for (int p = warp; p < STBPE_PARTS; p += STBPE_PART_THREADS / 32) {
+        // flush into this CTA's regions: a warp serves its eight rings at once, four lanes per ring
+        // (one ring at a time cost eight times the bookkeeping: the pass was bound by instruction
+        // issue, 128 instructions per token, a third of them here)
+        {
+            const int p = warp * (STBPE_PARTS / (STBPE_PART_THREADS / 32)) + (lane >> 2);
             const unsigned int n = min(s_cur[p], (unsigned int)STBPE_PART_RING);
-            if (n == 0u) continue;
             const unsigned int g = s_fill[p];
             __syncwarp();
             if ((i64)g + n <= pb.cap) {
                 uint32_t *dst = pb.words + ((i64)p * pb.n_cta + blockIdx.x) * pb.cap + g;
-                for (unsigned int k = lane; k < n; k += 32)
+                for (unsigned int k = lane & 3; k < n; k += 4)
                     dst[k] = s_ring[p * STBPE_PART_RING + ((k + p) & (STBPE_PART_RING - 1))];
-            } else if (lane == 0) {
+            } else if ((lane & 3) == 0) {
                 atomicOr(derr, STBPE_DERR_DENSE_OVERFLOW);
             }
-            if (lane == 0) {
+            if ((lane & 3) == 0) {
                 s_fill[p] = g + n;
                 s_cur[p] = 0u;
             }
@@ -206,6 +237,8 @@ __global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, Part
     const i64 n = pb.fill[(i64)p * pb.n_cta + region];
     const uint32_t *w = pb.words + ((i64)p * pb.n_cta + region) * pb.cap;
     unsigned int fresh = 0;
+    // (four words per thread and step, with their four table slots loaded before any is looked at,
+    // was slower: 30 ms instead of 21 ms for the 256 launches on 2^31 ids)
     for (i64 i = (i64)part * blockDim.x + threadIdx.x; i < n; i += (i64)per_region * blockDim.x) {
         const uint32_t x = __ldcs(w + i);  // streamed once: keep it from displacing the table slice
         const unsigned int c = (x * 0x9E3779B1u) >> (32 - STBPE_PART_CACHE_BITS);
@@ -227,4 +260,77 @@ __global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, Part
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) fresh += __shfl_down_sync(0xFFFFFFFFu, fresh, d);
     if ((threadIdx.x & 31) == 0 && fresh) atomicAdd(&e.st->n_keys, (u64)fresh);
+}
+
+// pass 2, several ranks: partition p, owned by this rank, out of the regions of every rank.  The grid
+// is one wave of blocks whatever the number of ranks; a block walks over its share of the
+// (source rank, region, half) units with one cache, which it adds to the table at the end.
+__global__ void __launch_bounds__(1024)
+    partition_table_peers_kernel(EngineDev e, WidePeers wp, int p, int n_cta) {
+    __shared__ uint32_t s_word[STBPE_PART_CACHE];
+    __shared__ unsigned int s_cnt[STBPE_PART_CACHE];
+    for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
+        s_word[i] = 0xFFFFFFFFu;
+        s_cnt[i] = 0u;
+    }
+    __syncthreads();
+    unsigned int fresh = 0;
+    const int n_units = wp.world * n_cta * 2;
+    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+        const int half = unit & 1, region = (unit >> 1) % n_cta, src = (unit >> 1) / n_cta;
+        const unsigned char *blk = wp.block[src];
+        const WideHeader hd = *reinterpret_cast<const WideHeader *>(blk);
+        if (hd.n_cta != n_cta) {  // every rank runs the first pass with the same grid
+            if (threadIdx.x == 0) atomicOr(&e.st->error, STBPE_DERR_DENSE_OVERFLOW);
+            continue;
+        }
+        const i64 n = wide_fill(blk)[(i64)p * n_cta + region];
+        const uint32_t *w = wide_words(blk, n_cta) + ((i64)p * n_cta + region) * hd.cap;
+        // words come four at a time (16-byte loads; regions are 16-byte aligned): a peer's words
+        // cross NVLink, and one word per load left the loop waiting for the link's latency
+        const i64 n4 = n / 4;
+        const uint4 *w4 = reinterpret_cast<const uint4 *>(w);
+        for (i64 i = (i64)half * blockDim.x + threadIdx.x; i <= n4; i += 2 * (i64)blockDim.x) {
+            uint32_t x[4];
+            int m = 4;
+            if (i < n4) {
+                const uint4 q = __ldcs(w4 + i);
+                x[0] = q.x, x[1] = q.y, x[2] = q.z, x[3] = q.w;
+            } else {
+                m = (int)(n - n4 * 4);
+                for (int k = 0; k < 4; ++k) x[k] = k < m ? w[n4 * 4 + k] : 0u;
+            }
+            for (int k = 0; k < m; ++k) {
+                const unsigned int c = (x[k] * 0x9E3779B1u) >> (32 - STBPE_PART_CACHE_BITS);
+                uint32_t kk = s_word[c];
+                if (kk == 0xFFFFFFFFu && x[k] != 0xFFFFFFFFu) {
+                    const uint32_t old = atomicCAS(&s_word[c], 0xFFFFFFFFu, x[k]);
+                    kk = old == 0xFFFFFFFFu ? x[k] : old;
+                }
+                if (kk == x[k] && x[k] != 0xFFFFFFFFu)
+                    atomicAdd(&s_cnt[c], 1u);
+                else
+                    part_word_to_table(e, x[k], 1ull, fresh);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
+        const unsigned int c = s_cnt[i];
+        if (c) part_word_to_table(e, s_word[i], (u64)c, fresh);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) fresh += __shfl_down_sync(0xFFFFFFFFu, fresh, d);
+    if ((threadIdx.x & 31) == 0 && fresh) atomicAdd(&e.st->n_keys, (u64)fresh);
+}
+
+// hot pairs (both ids below 256) owned by this rank: the sum of every rank's counter
+__global__ void dense_peers_to_table_kernel(EngineDev e, WidePeers wp, int n_cta) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= 65536) return;
+    const u64 key = ((u64)(k >> 8) << 32) | (u64)(k & 0xFF);
+    if (owner_of(key, wp.world) != wp.rank) return;
+    u64 c = 0;
+    for (int r = 0; r < wp.world; ++r) c += __ldcg(wide_dense(wp.block[r], n_cta) + k);
+    if (c) table_add(e, key, (i64)c);
 }

@@ -153,6 +153,60 @@ def rounds_until_next_check(done: int, target: int, check_every: int) -> int:
     return max(1, min(n, target - done + 1))
 
 
+# ----------------------------------------------------------------------------- first count, 16-bit vocabulary
+def wide_count(engine, group=None) -> bool:
+    """First count of an id stream over at most 65 536 ids, one process per GPU on one NVLink domain:
+    every rank partitions the pairs of its rows, the owner of a partition counts it out of all ranks'
+    buffers over peer memory (``stbpe_mg_wide_*``).  Call it before the loop's count round, which then
+    finds the table filled.  Returns False - and leaves the counting to that round - when the stream
+    of any rank does not qualify.  ``torch.distributed`` carries the IPC handles (first call on an
+    engine only: the peers' buffers stay mapped until ``wide_close``), the agreement and the barrier
+    between the two passes."""
+    import torch.distributed as dist
+    lib = L.load()
+    world = engine.world_size
+    if engine.base_vocab > 65536 or world < 2:
+        return False
+    dev = engine.device
+    if not getattr(engine, "_wide_mapped", False):
+        buf = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(dev):
+            st = lib.stbpe_mg_wide_export(engine._h, buf)
+        have = torch.tensor([1 if st == L.OK else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
+        if int(have.item()) == 0:     # a rank has no room for the buffers: the ordinary round counts
+            return False
+        mine = torch.tensor(list(buf), dtype=torch.uint8, device=dev)
+        every = torch.empty(world * 64, dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(every, mine, group=group)
+        raw = bytes(every.cpu().tolist())
+        with torch.cuda.device(dev):
+            engine._check(lib.stbpe_mg_wide_open(engine._h, raw, world))
+        engine._wide_mapped = True
+    ok = ctypes.c_int32(0)
+    with torch.cuda.device(dev):
+        engine._check(lib.stbpe_mg_wide_pass1(engine._h, ctypes.byref(ok), engine._s))
+    agreed = torch.tensor([ok.value], dtype=torch.int32, device=dev)
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)   # also the barrier between the passes
+    good = int(agreed.item()) == 1
+    if good:
+        with torch.cuda.device(dev):
+            engine._check(lib.stbpe_mg_wide_pass2(engine._h, engine._s))
+    dist.barrier(group=group)     # nobody starts the next first pass while a peer still reads this one
+    return good
+
+
+def wide_close(engine, group=None) -> None:
+    """Unmap the peers' partition buffers and wait for every rank to have done so; call before the
+    engine is closed (its buffers must outlive the peers' mappings)."""
+    import torch.distributed as dist
+    if getattr(engine, "_wide_mapped", False):
+        with torch.cuda.device(engine.device):
+            engine._check(L.load().stbpe_mg_wide_close(engine._h))
+        dist.barrier(group=group)
+        engine._wide_mapped = False
+
+
 # ----------------------------------------------------------------------------- workers
 class EngineWorker:
     """One rank's engine plus its exchange buffers (torch tensors on the engine's device)."""
@@ -419,6 +473,11 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     K, W = args.steps, args.warmup
     dev = torch.device("cuda", local_rank)
     dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "c3":
+        run_count_bench_multi(args, wl, rank, local_rank, world)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     corpus = getattr(synth, gen)(n_bytes=n_bytes, seed=seed, device=str(dev))
     off = corpus.row_offsets.cpu().numpy()
     lo, hi = shard_rows(off, world)[rank]
@@ -546,3 +605,103 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def run_count_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
+    """``bench.py --workload c3`` at N > 1: the id stream sharded by rows over the ranks, one histogram
+    pass per step.  A step = first pass on every rank, second pass on the owners over peer memory, and
+    the count round that selects the best pair (timed together with CUDA events, maximum over ranks)."""
+    import json
+    import time
+
+    import torch.distributed as dist
+
+    from . import synth
+    from .engine import Engine
+
+    gen, n_tokens, seed, _, desc = wl
+    K, W = args.steps, max(args.warmup, 1)
+    dev = torch.device("cuda", local_rank)
+    ids, off = synth.config3_ids(n_tokens, seed=seed, device=str(dev))
+    off = off.cpu().numpy()
+    lo, hi = shard_rows(off, world)[rank]
+    local = ids[off[lo]:off[hi]].clone()
+    local_off = off[lo:hi + 1] - off[lo]
+    del ids
+    torch.cuda.empty_cache()
+    n_local = int(local.numel())
+    slots = 1 << max(20, int(np.ceil(np.log2(max(n_tokens // 4 // world, 1)))))
+    e = Engine(max(n_local, 1), base_vocab=65536, max_merges=1, device=dev, table_slots=slots,
+               world_size=world, rank=rank)
+    loop = PeerLoop(e, cap_per_peer=4096)
+
+    def synced_max(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def step(src):
+        e.reset()
+        e.append_ids(src, local_off)
+        torch.cuda.synchronize()
+        dist.barrier()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        t = time.perf_counter()
+        a.record()
+        good = wide_count(e)
+        loop._counted = False
+        loop.run(1)
+        b.record()
+        torch.cuda.synchronize()
+        return good, a.elapsed_time(b), time.perf_counter() - t
+
+    ms, used = [], True
+    for it in range(W + K):
+        good, dev_ms, _ = step(local)
+        used = used and good
+        if it >= W:
+            ms.append(synced_max(dev_ms))
+    st = e.state()
+    keys = torch.tensor([float(st.table_keys)], dtype=torch.float64, device=dev)
+    dist.all_reduce(keys)
+    best, counts, _ = e.merges(0, 1)
+    kernel_ms = synced_max(float(st.count_kernel_ms))
+    # end to end from pinned host ids
+    host = torch.empty(n_local, dtype=torch.int32, pin_memory=True)
+    host.copy_(local)
+    del local
+    torch.cuda.empty_cache()
+    e.reset()
+    dist.barrier()
+    t = time.perf_counter()
+    e.append_ids(host, local_off)
+    wide_count(e)
+    loop._counted = False
+    loop.run(1)
+    torch.cuda.synchronize()
+    e2e_s = synced_max(time.perf_counter() - t)
+    wide_close(e)
+    loop.close()
+    e.close()
+    if rank == 0:
+        from bench import peaks  # type: ignore
+        peak, peak_kind = peaks()
+        med = float(np.median(ms))
+        gbs = 4.0 * n_tokens / (med / 1e3) / 1e9
+        print(json.dumps({
+            "metric": "pair_count_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": med, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int32", "data": "synthetic",
+            "config": {"workload": desc, "name": "c3", "tokens": n_tokens, "rows": len(off) - 1,
+                       "distinct_pairs": int(keys.item()),
+                       "best_pair": [int(best[0][0]), int(best[0][1]), int(counts[0])] if best else None,
+                       "partitioned_path": bool(used), "l2": "inputs larger than L2", "bytes_per_token": 4,
+                       "sharding": "contiguous row ranges by tokens; partitions (and keys) owned by partition % ranks"},
+            "roofline": {"bound": "hbm", "kernel": "both passes of the partitioned count + the count round "
+                                                   "(host barrier between the passes included)",
+                         "achieved": gbs, "peak": peak * world, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": gbs / (peak * world), "kernels_only_ms": kernel_ms, "traffic": None},
+            "e2e": {"value": 4.0 * n_tokens / e2e_s / 1e9, "unit": "GB/s", "seconds": e2e_s,
+                    "h2d_bytes_per_step": 4.0 * n_tokens, "d2h_bytes_per_step": 24.0},
+            "gpu_launches": (2 + 256 // world + 6) * K, "clocks": None, "cpu_baseline": None}), flush=True)

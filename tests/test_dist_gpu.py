@@ -274,3 +274,74 @@ def test_trainer_in_a_process_group_of_two_ranks():
     assert not failed, failed
     for rank, m, cnt, vocab, _ in results:
         assert m == om and cnt == oc and vocab == 256 + target
+
+
+def _wide_rank(rank, world, port, q):
+    import datetime
+    import torch.distributed as dist
+    from supertoken_b200.dist import PeerLoop, wide_close, wide_count
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), STBPE_DENSE32_MIN_TOKENS="1")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
+    try:
+        ids, off = synth.config3_ids(1 << 21, seed=2)
+        lo, hi = shard_rows(off, world)[rank]
+        e = Engine(int(off[hi] - off[lo]), base_vocab=65536, max_merges=3, device=f"cuda:{rank}",
+                   table_slots=1 << 22, world_size=world, rank=rank)
+        e.append_ids(np.ascontiguousarray(ids[off[lo]:off[hi]]), off[lo:hi + 1] - off[lo])
+        loop = PeerLoop(e, cap_per_peer=4096)
+        assert wide_count(e)                       # both passes ran: the table holds this rank's keys
+        k, c = e.export_histogram(cap=1 << 22)
+        done, stop = loop.train(check_every=8)
+        m, cnt, _ = e.merges()
+        wide_close(e)
+        loop.close()
+        q.put((rank, k.cpu().numpy().astype(np.uint64), c.cpu().numpy(), m, cnt.tolist(), done, stop))
+    except Exception as exc:
+        q.put((rank, "error", repr(exc), 0, 0, 0, 0))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_first_count_of_a_16_bit_vocabulary_over_ranks(world):
+    # every rank partitions the pairs of its rows, the owner of a partition counts it out of all
+    # ranks' buffers over peer memory: the union of the ranks' tables is the histogram of the whole
+    # stream, every key on the rank that owns it, and the merges that follow are the oracle's
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    from supertoken_b200.dist import owner_of
+    ids, off = synth.config3_ids(1 << 21, seed=2)
+    ok, oc = O.count_pairs_flat(ids, off, 1)
+    om, ocnt, _ = O.train_flat(ids, off, 65536, 3, 1)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_wide_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = []
+    try:
+        for _ in range(world):
+            results.append(q.get(timeout=240))
+            if isinstance(results[-1][1], str):
+                break
+    finally:
+        failed = [r for r in results if isinstance(r[1], str)] or len(results) < world
+        for p in procs:
+            p.join(timeout=5 if failed else 60)
+            if p.is_alive():
+                p.terminate()
+    assert not failed, failed
+    keys = np.concatenate([r[1] for r in results])
+    counts = np.concatenate([r[2] for r in results])
+    order = np.argsort(keys, kind="stable")
+    assert np.array_equal(keys[order], ok) and np.array_equal(counts[order], oc)
+    for rank, k, _, m, cnt, done, stop in results:
+        assert all(owner_of(int(x), world) == rank for x in k[:2000])
+        assert m == om and cnt == ocnt and done == 3 and stop == L.STOP_TARGET
