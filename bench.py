@@ -514,7 +514,7 @@ def main():
         "e2e": {"value": e2e, "unit": "merges/s", "seconds": e2e_s,
                 "h2d_bytes_per_step": (n_tokens + off_np.nbytes) / max(len(learned), 1),
                 "d2h_bytes_per_step": 24.0},
-        "gpu_launches": 2 * done + 2,   # decide_kernel + merge_kernel per merge, count and the final decision
+        "gpu_launches": 4 * done + 2,   # select, worklist, merge, refresh per merge; the count and the final selection
         "clocks": clocks,
         "cpu_baseline": cpu,
     }

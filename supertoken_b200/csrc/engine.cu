@@ -668,20 +668,13 @@ STBPE_VISIBLE int stbpe_select_best(stbpe_engine *e, uint64_t *key, int64_t *cou
 
 static int filter_policy(stbpe_engine *e, const DevState &h, bool layout_changed, cudaStream_t s);
 
-// The one CTA that ends decide_kernel can also build the worklist, which saves a launch, but it
-// walks the filter rows alone: measured on 2^20 tiles, 200-400 us per merge instead of 9 us for the
-// 32-CTA worklist_kernel.  Only streams of a few thousand tiles take that route.
-static bool worklist_in_decide(const stbpe_engine *e) { return (e->d.n_tiles + 31) / 32 <= 256; }
-
-static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s, bool have_worklist = false) {
+static int launch_merge(stbpe_engine *e, bool mg, cudaStream_t s) {
     if (e->d.n_tiles > 0) {
-        if (!have_worklist) {
-            const int wl_words = (e->d.n_tiles + 31) / 32;
-            int wl_grid = (wl_words + 1023) / 1024;
-            if (wl_grid > 32) wl_grid = 32;
-            worklist_kernel<<<wl_grid, 1024, 0, s>>>(e->d);
-            CK(cudaGetLastError());
-        }
+        const int wl_words = (e->d.n_tiles + 31) / 32;
+        int wl_grid = (wl_words + 1023) / 1024;
+        if (wl_grid > 32) wl_grid = 32;
+        worklist_kernel<<<wl_grid, 1024, 0, s>>>(e->d);
+        CK(cudaGetLastError());
         int grid = e->merge_grid < e->d.n_tiles ? e->merge_grid : e->d.n_tiles;
         if (mg)
             merge_kernel<true><<<grid, STBPE_CTA_THREADS, e->merge_smem, s>>>(e->d, e->merge_slots);
@@ -805,19 +798,16 @@ __global__ void set_target_kernel(EngineDev e, int target) {
     e.st->n_matches = 0;
 }
 
-// one iteration of the single-GPU loop: two launches (three when the worklist is too long for one CTA)
+// One iteration of the single-GPU loop: select, worklist, merge, refresh.  (Folding refresh, select
+// and the worklist into one launch was tried: the CTA that finishes last then recomputes the dirty
+// super-block maxima and walks the filter rows alone, and since early in a run nearly every
+// super-block is dirty that took 85-400 us per merge instead of the 30 us of the three launches.)
 static int enqueue_iteration(stbpe_engine *e, cudaStream_t s) {
-    const bool wl = worklist_in_decide(e);
-    decide_kernel<<<e->refresh_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, wl ? 1 : 0);
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
     CK(cudaGetLastError());
-    return launch_merge(e, false, s, wl);
-}
-
-// the step that ends a batch of iterations: maxima of the last merge's blocks, next selection or stop rule
-static int enqueue_final_decide(stbpe_engine *e, cudaStream_t s) {
-    decide_kernel<<<e->refresh_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 0);
-    CK(cudaGetLastError());
-    return STBPE_OK;
+    int rc = launch_merge(e, false, s);
+    if (rc != STBPE_OK) return rc;
+    return launch_refresh(e, 0, s);
 }
 
 STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
@@ -889,12 +879,9 @@ STBPE_VISIBLE int stbpe_train(stbpe_engine *e, int32_t n_merges, void *stream) {
             if (h.stopped) break;
         }
     }
-    // one more decision refreshes the maxima of the last merge and gives the stop reason without
-    // applying anything when the target is reached
-    {
-        int rc = enqueue_final_decide(e, s);
-        if (rc != STBPE_OK) return rc;
-    }
+    // one more selection decides the stop reason without applying anything when the target is reached
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
+    CK(cudaGetLastError());
     CK(cudaStreamSynchronize(s));
     return check_device_error(e, s);
 }
@@ -940,14 +927,14 @@ STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *ke
         }
         const int step = (e->filter_valid || e->d.n_tiles < 64) ? P : 32;
         n = todo - base < step ? todo - base : step;
-        const bool wl = worklist_in_decide(e);
         for (int i = 0; i < n && rc == STBPE_OK; ++i) {
             cudaEventRecord(ev[4 * i], s);
-            decide_kernel<<<e->refresh_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, wl ? 1 : 0);
+            select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
             cudaEventRecord(ev[4 * i + 1], s);
-            rc = launch_merge(e, false, s, wl);
+            rc = launch_merge(e, false, s);
             cudaEventRecord(ev[4 * i + 2], s);
-            cudaEventRecord(ev[4 * i + 3], s);  // the refresh is part of the next decide_kernel
+            if (rc == STBPE_OK) rc = launch_refresh(e, 0, s);
+            cudaEventRecord(ev[4 * i + 3], s);
         }
         cudaStreamSynchronize(s);
         for (int i = 0; i < n && rc == STBPE_OK; ++i)
@@ -961,8 +948,8 @@ STBPE_VISIBLE int stbpe_train_timed(stbpe_engine *e, int32_t n_merges, float *ke
     cudaEventDestroy(r0);
     cudaEventDestroy(r1);
     if (rc != STBPE_OK) return rc;
-    rc = enqueue_final_decide(e, s);
-    if (rc != STBPE_OK) return rc;
+    select_kernel<<<e->select_grid, STBPE_SELECT_THREADS, 0, s>>>(e->d, 1, 0, e->cand);
+    CK(cudaGetLastError());
     CK(cudaStreamSynchronize(s));
     return check_device_error(e, s);
 }

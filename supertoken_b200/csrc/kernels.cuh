@@ -488,54 +488,6 @@ __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
     build_worklist(e, blockIdx.x, gridDim.x);
 }
 
-// The single-GPU loop's step between two merges in one launch: block maxima of the blocks the last
-// merge touched (all CTAs), then, in the CTA that finishes last, the super-block maxima, the
-// arg-max, the bookkeeping of the selected merge (or a stop rule) and, with `with_worklist`, the
-// tiles it has to visit (short streams only: one CTA walks the filter rows far slower than the
-// 32-CTA worklist_kernel).  As separate launches refresh and select took 9 + 14 us of a 70 us merge
-// late in a run, most of it launch latency and dependent round trips to memory.
-__global__ void __launch_bounds__(STBPE_SELECT_THREADS) decide_kernel(EngineDev e, int with_worklist) {
-    DevState *st = e.st;
-    if (st->stopped) return;
-    __shared__ u64 s_k[STBPE_SELECT_THREADS / 32];
-    __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
-    __shared__ int s_last;
-    refresh_blocks(e, 0, min(st->n_dirty, e.n_blocks), (blockIdx.x * blockDim.x + threadIdx.x) >> 5,
-                   (gridDim.x * blockDim.x) >> 5);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        s_last = (atomicAdd(&st->ticket, 1u) == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    refresh_super_blocks(e, 0, min(*(volatile unsigned int *)&st->n_dirty2, e.n_super2), threadIdx.x >> 5,
-                         STBPE_SELECT_THREADS / 32);
-    __syncthreads();
-    u64 bk = STBPE_EMPTY;
-    i64 bc = 0;
-    for (unsigned int i = threadIdx.x; i < e.n_super2; i += STBPE_SELECT_THREADS) {
-        const volatile Slot *p = e.supermax + i;
-        const u64 k = p->key;
-        const i64 c = p->count;
-        if (c > 0 && better(k, c, bk, bc)) {
-            bk = k;
-            bc = c;
-        }
-    }
-    block_best(bk, bc, s_k, s_c);
-    if (threadIdx.x == 0) {
-        st->ticket = 0;
-        st->n_dirty2 = 0;
-        advance_or_stop(e, bk, bc);
-        if (!st->stopped && !st->filter_valid) st->n_work = -1;  // stale filter: every tile
-        __threadfence();
-    }
-    __syncthreads();
-    if (with_worklist && !*(volatile int *)&st->stopped && *(volatile int *)&st->filter_valid) build_worklist(e, 0, 1);
-}
-
 // (Re)build the pair filter from the stream: after a load and after every re-pack.  One CTA handles
 // 32 consecutive tiles, i.e. one word of every row: it collects the bits in shared memory and then
 // writes the STBPE_PROWS words with plain stores.
