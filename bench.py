@@ -288,6 +288,14 @@ def count_bench(wl, dev, K, W, with_e2e=True):
     clocks = sampler.stop()
     st = eng.state()
     key, count, ties = eng.select_best(True)
+    # size-independent check of the whole histogram: every pair position is counted exactly once
+    # (tokens minus non-empty rows), and the exported keys are strictly ascending (no key twice)
+    hk, hc = eng.export_histogram()
+    n_pairs = n_tokens - int(np.count_nonzero(np.diff(off_np)))
+    sum_ok = bool(int(hc.sum().item()) == n_pairs and hk.numel() == st.table_keys
+                  and bool((hk[1:] > hk[:-1]).all().item()))
+    del hk, hc
+    torch.cuda.empty_cache()
     peak, peak_kind = peaks()
     med = float(np.median(ms))
     gbs = 4.0 * n_tokens / (med / 1e3) / 1e9
@@ -315,6 +323,7 @@ def count_bench(wl, dev, K, W, with_e2e=True):
         "dtype": "int32", "data": "synthetic",
         "config": {"workload": desc, "name": "c3", "tokens": n_tokens, "rows": len(off_np) - 1,
                    "distinct_pairs": int(st.table_keys), "best_pair": [int(key >> 32), int(key & 0xFFFFFFFF), int(count)],
+                   "sum_of_counts_equals_pair_positions": sum_ok,
                    "l2": "inputs larger than L2", "bytes_per_token": 4},
         "roofline": {"bound": "hbm",
                      "kernel": ("partition_pairs_kernel + 256 x partition_table_kernel: both passes, until the "
@@ -487,6 +496,7 @@ def main():
                          "second_pass_ms": c3["roofline"]["second_pass_ms"], "kernel": c3["roofline"]["kernel"],
                          "frac_of_measured_peak": c3["roofline"]["frac"], "frac_of_8tbs": c3["roofline"]["frac_of_8tbs"],
                          "distinct_pairs": c3["config"]["distinct_pairs"], "best_pair": c3["config"]["best_pair"],
+                         "sum_of_counts_equals_pair_positions": c3["config"]["sum_of_counts_equals_pair_positions"],
                          "bytes_per_token": 4}
 
     line = {
