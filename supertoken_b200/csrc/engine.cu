@@ -118,7 +118,7 @@ static bool is_device_pointer(const void *p) {
 
 extern "C" {
 
-STBPE_VISIBLE const char *stbpe_version(void) { return "stbpe 0.1 (sm_100a)"; }
+STBPE_VISIBLE const char *stbpe_version(void) { return "stbpe 0.2 (sm_100a)"; }
 
 STBPE_VISIBLE const char *stbpe_last_error(const stbpe_engine *e) {
     return e ? e->err.c_str() : g_create_err.c_str();
@@ -420,7 +420,7 @@ static int check_device_error(stbpe_engine *e, cudaStream_t s) {
     if (err & STBPE_DERR_BAD_ID)
         return fail(e, STBPE_E_ID_OVERFLOW, "Token id overflow: ids must be in [0, 2^31-2]");
     if (err & STBPE_DERR_TABLE_FULL)
-        return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (pair table full)");
+        return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (pair table full: create the engine with more table_slots, GPUBPETrainer.table_slots)");
     if (err & STBPE_DERR_OUTBOX_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (delta outbox full)");
     if (err & STBPE_DERR_LTABLE_FULL) return fail(e, STBPE_E_CAPACITY, "pair workspace capacity exceeded (local delta table full)");
     if (err & STBPE_DERR_TIMEOUT) return fail(e, STBPE_E_TIMEOUT, "a bounded device-side wait gave up (tile pipeline or a peer's flag)");
