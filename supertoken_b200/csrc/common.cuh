@@ -199,6 +199,16 @@ __device__ __forceinline__ u64 slot_of(const EngineDev &e, u64 key) {
     return ((u64)part_of(key) << e.slot_bits) | (mix64(key) >> (64 - e.slot_bits));
 }
 
+// Programmatic dependent launch: inside the captured loop every kernel is launched with the
+// programmatic-serialisation attribute, so its CTAs may become resident while the kernel before it
+// still runs.  dep_release() lets the next kernel's CTAs be scheduled as soon as all CTAs of this
+// one have started; dep_wait() returns when the kernel before this one has completed and its writes
+// are visible.  Every thread executes dep_wait() before it touches global memory or returns (a
+// kernel that ended without waiting would complete before its predecessor).  Launched without the
+// attribute both are no-ops.
+__device__ __forceinline__ void dep_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ bool better(u64 k1, i64 c1, u64 k2, i64 c2) {
     // (k1, c1) beats (k2, c2): larger count, ties to the smaller packed key
     // (gpu_tokenizer/trainers/bpe_gpu.py:106-127)
@@ -218,6 +228,11 @@ __device__ __forceinline__ void mark_dirty(const EngineDev &e, u64 slot_index) {
 // add delta to key in the pair table, inserting the key when absent
 __device__ __forceinline__ void table_add(const EngineDev &e, u64 key, i64 delta) {
     u64 h = slot_of(e, key);
+    // the recorded maximum and the dirty flag of the block the key hashes to, fetched together with
+    // the first probe (a key that was pushed into the next block re-reads them below)
+    const u64 blk0 = h / STBPE_BLK;
+    uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(e.blockmax + blk0));
+    unsigned int flagged = *(volatile unsigned int *)&e.dirty_flag[blk0];
     for (unsigned int probe = 0; probe < STBPE_MAX_PROBE; ++probe) {
         Slot *s = &e.table[h];
         u64 k = *(volatile u64 *)&s->key;
@@ -236,10 +251,13 @@ __device__ __forceinline__ void table_add(const EngineDev &e, u64 key, i64 delta
             // if its count now reaches it (the add that brings a key to its final count sees that
             // count, because the adds on one slot are serialised; the recorded maxima do not change
             // while deltas are applied).  Only those blocks are recomputed by refresh_kernel.
-            const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(e.blockmax + (h / STBPE_BLK)));
+            if (h / STBPE_BLK != blk0) {
+                raw = __ldcg(reinterpret_cast<const uint4 *>(e.blockmax + (h / STBPE_BLK)));
+                flagged = 0u;
+            }
             const u64 mk = ((u64)raw.y << 32) | raw.x;
             const i64 mc = (i64)(((u64)raw.w << 32) | raw.z);
-            if (key == mk || now > mc || (now == mc && key < mk)) mark_dirty(e, h);
+            if (!flagged && (key == mk || now > mc || (now == mc && key < mk))) mark_dirty(e, h);
             return;
         }
         h = (h + 1) & e.mask;
@@ -437,15 +455,21 @@ __device__ __forceinline__ int current_rec(const EngineDev &e, int tile, int m, 
 
 // Live tokens around a tile, in stream order: the last two live tokens before it and up to
 // three live tokens after it (STBPE_NONE where the stream ends).  Walks records only.
+// `before` / `after`: the records of tiles tile - 1 and tile + 1 when the caller has loaded them
+// already (together with the tile's own, so that the three look-ups are one round trip).
 __device__ __forceinline__ void gather_halo(const EngineDev &e, int tile, int m, uint32_t &prev,
-                                            uint32_t &prev2, uint32_t nxt[3], int &next_tile, int &prev_tile) {
+                                            uint32_t &prev2, uint32_t nxt[3], int &next_tile, int &prev_tile,
+                                            const TileRec *before = nullptr, const TileRec *after = nullptr) {
     next_tile = prev_tile = -1;
     prev = prev2 = STBPE_NONE;
     nxt[0] = nxt[1] = nxt[2] = STBPE_NONE;
     TileRec r;
     int back = 0;
     for (int t = tile - 1; t >= 0 && back < 2; --t) {
-        current_rec(e, t, m, r);
+        if (before && t == tile - 1)
+            r = *before;
+        else
+            current_rec(e, t, m, r);
         if (r.len > 0) {
             if (back == 0) {
                 prev = r.tail;
@@ -463,7 +487,10 @@ __device__ __forceinline__ void gather_halo(const EngineDev &e, int tile, int m,
     }
     int have = 0;
     for (int t = tile + 1; t < e.n_tiles && have < 3; ++t) {
-        current_rec(e, t, m, r);
+        if (after && t == tile + 1)
+            r = *after;
+        else
+            current_rec(e, t, m, r);
         int take = r.len < 3 ? r.len : 3;
         if (take > 0 && next_tile < 0) next_tile = t;
         for (int i = 0; i < take && have < 3; ++i) nxt[have++] = r.head[i];

@@ -242,6 +242,8 @@ __device__ __forceinline__ void refresh_blocks(const EngineDev &e, int all, unsi
 }
 
 __global__ void refresh_kernel(EngineDev e, int all) {
+    dep_release();
+    dep_wait();
     const unsigned int n = all ? e.n_blocks : min(e.st->n_dirty, e.n_blocks);
     refresh_blocks(e, all, n, (blockIdx.x * blockDim.x + threadIdx.x) >> 5, (gridDim.x * blockDim.x) >> 5);
 }
@@ -381,12 +383,16 @@ __device__ __forceinline__ void refresh_super_blocks(const EngineDev &e, int all
 // and commit (target = the merge target of the engine)
 __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
     select_kernel(EngineDev e, int mode, int all2, i64 *cand, int target = 0) {
+    dep_release();
+    dep_wait();
     DevState *st = e.st;
-    if (mode == 1 && st->stopped) return;
+    const int stopped = st->stopped;            // both in one round trip
+    const unsigned int n_dirty2 = st->n_dirty2;
+    if (mode == 1 && stopped) return;
     __shared__ u64 s_k[STBPE_SELECT_THREADS / 32];
     __shared__ i64 s_c[STBPE_SELECT_THREADS / 32];
     __shared__ int s_last;
-    const unsigned int n2 = all2 ? e.n_super2 : min(st->n_dirty2, e.n_super2);
+    const unsigned int n2 = all2 ? e.n_super2 : min(n_dirty2, e.n_super2);
     refresh_super_blocks(e, all2, n2, blockIdx.x * (STBPE_SELECT_THREADS / 32) + (threadIdx.x >> 5),
                          gridDim.x * (STBPE_SELECT_THREADS / 32));
     __syncthreads();
@@ -439,10 +445,10 @@ __global__ void __launch_bounds__(STBPE_SELECT_THREADS)
 // ---------------------------------------------------------------------------------------
 // the tiles merge (cur_a, cur_b) must visit: bitmap and compact list; `block` of `n_blocks` thread
 // blocks of blockDim.x threads share the words of the bitmap
-__device__ __forceinline__ void build_worklist(const EngineDev &e, int block, int n_blocks) {
+__device__ __forceinline__ void build_worklist(const EngineDev &e, int block, int n_blocks, int cur_a, int cur_b) {
     DevState *st = e.st;
     unsigned int r1, r2, r3;
-    filter_rows(((u64)(uint32_t)st->cur_a << 32) | (u64)(uint32_t)st->cur_b, r1, r2, r3);
+    filter_rows(((u64)(uint32_t)cur_a << 32) | (u64)(uint32_t)cur_b, r1, r2, r3);
     const unsigned int *row1 = e.presence + (size_t)r1 * e.presence_words;
     const unsigned int *row2 = e.presence + (size_t)r2 * e.presence_words;
     const unsigned int *row3 = e.presence + (size_t)r3 * e.presence_words;
@@ -479,13 +485,17 @@ __device__ __forceinline__ void build_worklist(const EngineDev &e, int block, in
 }
 
 __global__ void __launch_bounds__(1024) worklist_kernel(EngineDev e) {
+    dep_release();
+    dep_wait();
     DevState *st = e.st;
-    if (st->stopped || st->exchange_only) return;
-    if (!st->filter_valid) {  // stale filter: the merge visits every tile
+    const int stopped = st->stopped, exchange_only = st->exchange_only, filter_valid = st->filter_valid;
+    const int cur_a = st->cur_a, cur_b = st->cur_b;  // all in one round trip
+    if (stopped || exchange_only) return;
+    if (!filter_valid) {  // stale filter: the merge visits every tile
         if (blockIdx.x == 0 && threadIdx.x == 0) st->n_work = -1;
         return;
     }
-    build_worklist(e, blockIdx.x, gridDim.x);
+    build_worklist(e, blockIdx.x, gridDim.x, cur_a, cur_b);
 }
 
 // (Re)build the pair filter from the stream: after a load and after every re-pack.  One CTA handles

@@ -154,7 +154,9 @@ __device__ __forceinline__ void pipe_setup(TilePipe &pipe) {
 // Producer warp: feeds this CTA's tiles through the ring, then one end marker per consumer warp.
 // n_work < 0: tiles blockIdx.x, +gridDim.x, ...; otherwise the tiles listed in worklist items
 // blockIdx.x, +gridDim.x, ...
-__device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe, int m, int lane, int n_work) {
+// `first_item`: worklist item blockIdx.x + lane * gridDim.x, read by the caller ahead of n_work.
+__device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe, int m, int lane, int n_work,
+                                              unsigned int first_item) {
     unsigned int *derr = &e.st->error;
     const unsigned int lt = (1u << lane) - 1u;
     int it_base = 0;
@@ -166,15 +168,22 @@ __device__ __forceinline__ void produce_tiles(const EngineDev &e, TilePipe &pipe
         const long long limit = n_work < 0 ? (long long)e.n_tiles : (long long)n_work;
         if (first >= limit) break;
         const long long mine = first + (long long)lane * gridDim.x;
-        if (mine < limit) tile = n_work < 0 ? (int)mine : (int)e.worklist[mine];
+        if (mine < limit) tile = n_work < 0 ? (int)mine : (j0 == 0 ? (int)first_item : (int)e.worklist[mine]);
         more = first + 32ll * gridDim.x < limit;
         TileRec rec;
         int slot = 0, len = 0, next_tile = -1, prev_tile = -1;
         uint32_t prev = STBPE_NONE, prev2 = STBPE_NONE, nxt[3] = {STBPE_NONE, STBPE_NONE, STBPE_NONE};
         if (tile >= 0) {
+            // the tile's records and its neighbours' are adjacent: one round trip for the three
+            TileRec before, after;
+            const bool has_before = tile > 0, has_after = tile + 1 < e.n_tiles;
             slot = current_rec(e, tile, m, rec);
+            if (has_before) current_rec(e, tile - 1, m, before);
+            if (has_after) current_rec(e, tile + 1, m, after);
             len = rec.len;
-            if (len > 0) gather_halo(e, tile, m, prev, prev2, nxt, next_tile, prev_tile);
+            if (len > 0)
+                gather_halo(e, tile, m, prev, prev2, nxt, next_tile, prev_tile, has_before ? &before : nullptr,
+                            has_after ? &after : nullptr);
         }
         const unsigned int has = __ballot_sync(0xFFFFFFFFu, len > 0);
         const int my_it = it_base + __popc(has & lt);
@@ -240,7 +249,7 @@ __global__ void __launch_bounds__(STBPE_CTA_THREADS, STBPE_MIN_CTAS) count_kerne
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m = 0x7FFFFFFF;  // every record version counts as "before"
     if (warp == STBPE_NCW) {
-        produce_tiles(e, pipe, m, lane, -1);
+        produce_tiles(e, pipe, m, lane, -1, 0u);
     } else {
         unsigned int *derr = &e.st->error;
         for (int it = warp;; it += STBPE_NCW) {
@@ -412,21 +421,33 @@ __device__ __forceinline__ void drain_queue(const SmemTable &tab, const EngineDe
 template <bool MG>
 __global__ void __launch_bounds__(STBPE_CTA_THREADS, STBPE_MIN_CTAS) merge_kernel(EngineDev e, unsigned int smem_slots) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    DevState *st = e.st;
-    if (st->stopped || st->exchange_only) return;
-    const uint32_t a = (uint32_t)st->cur_a, b = (uint32_t)st->cur_b, nw = (uint32_t)st->cur_new;
-    const int m = st->merges_done;  // number of this merge (>= 1)
-    if (m < 1) return;              // nothing has been selected yet
-    const bool same = (a == b);
-
+    // the shared-memory set-up needs nothing from the kernels before this one: inside the captured
+    // loop it runs while they finish
+    dep_release();
     TilePipe pipe;
     pipe.carve(smem_raw, smem_slots);
     pipe_setup(pipe);
+    dep_wait();
+    DevState *st = e.st;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // everything the kernel needs from the loop state in one round trip, and with it the producer
+    // warp's first worklist items (the list is as long as the stream has tiles; items past n_work
+    // are stale and not used)
+    const int stopped = st->stopped, exchange_only = st->exchange_only;
+    const uint32_t a = (uint32_t)st->cur_a, b = (uint32_t)st->cur_b, nw = (uint32_t)st->cur_new;
+    const int m = st->merges_done;  // number of this merge (>= 1)
     const int n_work = st->n_work;  // < 0: every tile
     const bool fv = st->filter_valid != 0;  // the pair filter is being maintained
+    unsigned int first_item = 0;
     if (warp == STBPE_NCW) {
-        produce_tiles(e, pipe, m, lane, n_work);
+        const long long mine = blockIdx.x + (long long)lane * gridDim.x;
+        if (mine < (long long)e.n_tiles) first_item = e.worklist[mine];
+    }
+    if (stopped || exchange_only) return;
+    if (m < 1) return;  // nothing has been selected yet
+    const bool same = (a == b);
+    if (warp == STBPE_NCW) {
+        produce_tiles(e, pipe, m, lane, n_work, first_item);
     } else {
         unsigned int *derr = &st->error;
         i64 removed = 0;
