@@ -7,7 +7,8 @@ One *step* is one merge of the loop (select best pair, rewrite the stream, updat
 histogram by deltas).  The workload at N=1 is the 1 GiB mixed-script corpus with a 32 000-merge
 target (seeded synthetic stand-in, generated on the device); ``--steps K`` times the first K
 merges of that job, the default K is the whole job.  Warm-up merges run first and the engine is
-then reloaded from the device-resident bytes, so the timed merges start from merge 0.
+then reloaded from the device-resident bytes, so the timed merges start from merge 0
+(``--first-merge M``: from merge M, after M untimed merges, to look at the late phase of a job).
 
 Printed JSON (one line, rank 0):
   value      merges/s with the corpus already packed in HBM (device time, CUDA events)
@@ -350,6 +351,9 @@ def main():
     ap.add_argument("--bytes", type=int, default=None, help="override the corpus size (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-c3", action="store_true", help="skip the config-3 pair-count block of the default run")
+    ap.add_argument("--first-merge", type=int, default=0,
+                    help="single GPU: run this many merges untimed after the count and time the --steps merges that "
+                         "follow (the late phase of a job); the end-to-end figure then covers all of them")
     args = ap.parse_args()
     wl = list(WORKLOADS[args.workload])
     if args.bytes:
@@ -383,7 +387,9 @@ def main():
         run_count_bench(args, wl, dev)
         return
 
-    K, W = args.steps, args.warmup
+    K, W, M = args.steps, args.warmup, max(args.first_merge, 0)
+    if M:
+        args.no_cpu_baseline = True   # the oracle would have to run the untimed merges first
     corpus = getattr(synth, gen)(n_bytes=n_bytes, seed=seed, device=str(dev))
     torch.cuda.synchronize()
     data_dev, off_np = corpus.data, corpus.row_offsets.cpu().numpy()
@@ -394,7 +400,7 @@ def main():
         e.record()
         return e
 
-    eng = Engine(n_tokens, base_vocab=256, max_merges=max(K, W, 1), device=dev)
+    eng = Engine(n_tokens, base_vocab=256, max_merges=max(M + K, W, 1), device=dev)
 
     def load():
         eng.reset()
@@ -412,18 +418,21 @@ def main():
     sampler.start()
     t0 = ev()
     eng.count_initial()
+    tc = ev()
+    if M:
+        eng.train(M)
     t1 = ev()
     eng.train(K)
     t2 = ev()
     torch.cuda.synchronize()
     clocks = sampler.stop()
-    count_call_ms = t0.elapsed_time(t1)
+    count_call_ms = t0.elapsed_time(tc)
     loop_ms = t1.elapsed_time(t2)
     st = eng.state()
     count_ms = float(st.count_kernel_ms)   # histogram kernel(s) only; the call also clears the table,
     # builds the tile records, the pair filter and the block maxima
-    done = st.merges_done
-    merges_gpu, counts_gpu, live_before = eng.merges(0, done)
+    done = st.merges_done - M
+    merges_gpu, counts_gpu, live_before = eng.merges(M, done)
     if done < 1:
         raise SystemExit("no merge was learned")
     value = done / (loop_ms / 1000.0)
@@ -431,11 +440,15 @@ def main():
     # per-kernel device time of the same K merges (events around every launch)
     load()
     eng.count_initial()
+    if M:
+        eng.train(M)
+    st_b = eng.state()
     sel_ms, mrg_ms, ref_ms, repack_ms = eng.train_timed(K)
     torch.cuda.synchronize()
     st_t = eng.state()
-    tile_bytes = float(st_t.tile_bytes_in + st_t.tile_bytes_out)   # what the merge kernel's bulk copies moved
-    merges_again, _, _ = eng.merges(0, eng.state().merges_done)
+    # what the merge kernel's bulk copies moved during the timed merges
+    tile_bytes = float(st_t.tile_bytes_in + st_t.tile_bytes_out) - float(st_b.tile_bytes_in + st_b.tile_bytes_out)
+    merges_again, _, _ = eng.merges(M, eng.state().merges_done - M)
     assert merges_again == merges_gpu, "merge list changed between two runs on the same input"
     algo_bytes = 4.0 * float(live_before.sum())
     peak, peak_kind = peaks()
@@ -450,12 +463,12 @@ def main():
     del data_dev, corpus
     torch.cuda.empty_cache()
     t = time.perf_counter()
-    trainer = GPUBPETrainer(base_vocab=256, merges=K, device=str(dev))
+    trainer = GPUBPETrainer(base_vocab=256, merges=M + K, device=str(dev))
     res = trainer.fit_bytes(host, off_np, log_every=0)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t
     learned = trainer.merge_counts
-    assert res["merges"][:len(learned)] == merges_gpu[:len(learned)]
+    assert res["merges"][M:len(learned)] == merges_gpu[:max(len(learned) - M, 0)]
     e2e = len(learned) / e2e_s
 
     cpu = None
@@ -504,7 +517,7 @@ def main():
         "warmup": W, "ms_per_step": loop_ms / done, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int32", "data": "synthetic",
         "config": {"workload": desc, "name": args.workload, "corpus_bytes": n_tokens, "rows": len(off_np) - 1,
-                   "merges_timed": done, "first_merge": 0, "stop_reason": int(st.stop_reason),
+                   "merges_timed": done, "first_merge": M, "stop_reason": int(st.stop_reason),
                    "merges_sha256": merges_sha256(merges_gpu, counts_gpu),
                    "oracle_prefix_ok": oracle_ok, "oracle_prefix_merges": oracle_n,
                    "l2": "inputs larger than L2 (4 bytes x tokens per merge)", "tile_tokens": 1024},

@@ -107,7 +107,7 @@ struct EngineDev {
     int n_tiles;
     Slot *table;
     u64 mask;
-    int slot_bits;  // log2(slots) - STBPE_PART_BITS: slot index bits below the partition
+    int slot_bits;  // slot index bits below the table slice of a partition (slots = slices << slot_bits)
     Slot *blockmax;
     unsigned int *dirty_flag;
     unsigned int *dirty_list;
@@ -194,9 +194,15 @@ __device__ __forceinline__ int owner_of(u64 key, int world) {
     return (int)(part_of(key) % (unsigned int)world);
 }
 
-// first slot probed for a key: partition in the top bits, then the top bits of the 64-bit mix
+// Table slice of a partition.  A rank holds only the keys it owns, i.e. the partitions with its
+// residue modulo the number of ranks: their slices are numbered densely (partition / ranks), so the
+// whole table is in use whatever the number of ranks.
+__device__ __forceinline__ unsigned int slice_of(const EngineDev &e, unsigned int part) {
+    return part / (unsigned int)e.world;
+}
+// first slot probed for a key: its partition's slice in the top bits, then the top bits of the 64-bit mix
 __device__ __forceinline__ u64 slot_of(const EngineDev &e, u64 key) {
-    return ((u64)part_of(key) << e.slot_bits) | (mix64(key) >> (64 - e.slot_bits));
+    return ((u64)slice_of(e, part_of(key)) << e.slot_bits) | (mix64(key) >> (64 - e.slot_bits));
 }
 
 // Programmatic dependent launch: inside the captured loop every kernel is launched with the

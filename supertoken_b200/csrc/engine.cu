@@ -254,8 +254,11 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     slots = next_pow2(slots < (u64)2 * STBPE_PARTS ? (u64)2 * STBPE_PARTS : slots);
     e->slots = slots;
     e->d.mask = slots - 1;
+    // table slices: one per partition this rank can own (partitions with its residue modulo the
+    // number of ranks), rounded up to a power of two
+    u64 slices = next_pow2(((u64)STBPE_PARTS + cfg->world_size - 1) / cfg->world_size);
     e->d.slot_bits = 0;
-    while ((1ull << (e->d.slot_bits + STBPE_PART_BITS)) < slots) ++e->d.slot_bits;
+    while ((slices << e->d.slot_bits) < slots) ++e->d.slot_bits;
     e->d.n_blocks = (unsigned int)(slots / STBPE_BLK);
     e->d.world = cfg->world_size;
     e->d.rank = cfg->rank;

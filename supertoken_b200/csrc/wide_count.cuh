@@ -212,10 +212,11 @@ __device__ __forceinline__ bool table_count_n(const EngineDev &e, u64 key, u64 h
     return false;
 }
 
-__device__ __forceinline__ void part_word_to_table(const EngineDev &e, uint32_t x, u64 n, unsigned int &fresh) {
+// `top`: the word's table slice shifted into place (every word of a pass-2 launch is of one partition)
+__device__ __forceinline__ void part_word_to_table(const EngineDev &e, uint32_t x, u64 n, unsigned int &fresh, u64 top) {
     const uint32_t ab = unmix32(x);
     const u64 key = ((u64)(ab >> 16) << 32) | (u64)(ab & 0xFFFFu);
-    const u64 h = ((u64)(x >> STBPE_PART_SHIFT) << e.slot_bits) | (mix64(key) >> (64 - e.slot_bits));
+    const u64 h = top | (mix64(key) >> (64 - e.slot_bits));
     table_count_n(e, key, h, n, fresh);
 }
 
@@ -234,6 +235,7 @@ __global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, Part
     }
     __syncthreads();
     const int region = blockIdx.x / per_region, part = blockIdx.x % per_region;
+    const u64 top = (u64)slice_of(e, (unsigned int)p) << e.slot_bits;
     const i64 n = pb.fill[(i64)p * pb.n_cta + region];
     const uint32_t *w = pb.words + ((i64)p * pb.n_cta + region) * pb.cap;
     unsigned int fresh = 0;
@@ -250,12 +252,12 @@ __global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, Part
         if (k == x && x != 0xFFFFFFFFu)
             atomicAdd(&s_cnt[c], 1u);
         else
-            part_word_to_table(e, x, 1ull, fresh);
+            part_word_to_table(e, x, 1ull, fresh, top);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
         const unsigned int c = s_cnt[i];
-        if (c) part_word_to_table(e, s_word[i], (u64)c, fresh);
+        if (c) part_word_to_table(e, s_word[i], (u64)c, fresh, top);
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) fresh += __shfl_down_sync(0xFFFFFFFFu, fresh, d);
@@ -275,6 +277,7 @@ __global__ void __launch_bounds__(1024)
     }
     __syncthreads();
     unsigned int fresh = 0;
+    const u64 top = (u64)slice_of(e, (unsigned int)p) << e.slot_bits;
     const int n_units = wp.world * n_cta * 2;
     for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
         const int half = unit & 1, region = (unit >> 1) % n_cta, src = (unit >> 1) / n_cta;
@@ -310,14 +313,14 @@ __global__ void __launch_bounds__(1024)
                 if (kk == x[k] && x[k] != 0xFFFFFFFFu)
                     atomicAdd(&s_cnt[c], 1u);
                 else
-                    part_word_to_table(e, x[k], 1ull, fresh);
+                    part_word_to_table(e, x[k], 1ull, fresh, top);
             }
         }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
         const unsigned int c = s_cnt[i];
-        if (c) part_word_to_table(e, s_word[i], (u64)c, fresh);
+        if (c) part_word_to_table(e, s_word[i], (u64)c, fresh, top);
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) fresh += __shfl_down_sync(0xFFFFFFFFu, fresh, d);

@@ -462,6 +462,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     """``bench.py`` at N > 1: the same corpus as N = 1, rows sharded over the ranks (strong
     scaling), one process per GPU over NCCL.  Rank 0 prints the JSON line."""
     import json
+    import sys
     import time
 
     import torch.distributed as dist
@@ -473,6 +474,12 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     K, W = args.steps, args.warmup
     dev = torch.device("cuda", local_rank)
     dist.init_process_group("nccl", device_id=dev)
+    t_start = time.perf_counter()
+
+    def phase(name: str) -> None:     # STBPE_BENCH_VERBOSE=1: wall-clock marks on stderr (rank 0)
+        if rank == 0 and os.environ.get("STBPE_BENCH_VERBOSE"):
+            print(f"[bench {time.perf_counter() - t_start:7.1f} s] {name}", file=sys.stderr, flush=True)
+
     if args.workload == "c3":
         run_count_bench_multi(args, wl, rank, local_rank, world)
         dist.barrier()
@@ -486,6 +493,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     del corpus
     torch.cuda.empty_cache()
     n_local = int(shard.numel())
+    phase("corpus generated and sharded")
 
     # round driver: kernels over peer memory (default), the native NCCL loop, or Python rounds
     driver = os.environ.get("STBPE_MG_DRIVER", "peer")
@@ -524,6 +532,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     loop.train(check_every=8)
     finish(e, loop)
     del e, loop
+    phase("warm-up done")
 
     e, loop = make(K)
     e.append_bytes(shard, shard_off)
@@ -546,6 +555,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     torch.cuda.synchronize()
     clocks = sampler.stop() if sampler is not None else None
     dist.barrier()
+    phase(f"timed run done ({done} merges, {loop.rounds} rounds)")
     count_ms = synced_max(t0.elapsed_time(t1))
     loop_ms = synced_max(t1.elapsed_time(t2))
     merges_gpu, counts_gpu, live_before = e.merges(0, done)
@@ -572,6 +582,7 @@ def run_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> None:
     e2e_s = synced_max((time.perf_counter() - t) * 1000.0) / 1000.0
     assert m2 == merges_gpu, "merge list changed between two runs on the same input"
     finish(e, loop2)
+    phase("end-to-end run done")
 
     if rank == 0:
         from bench import merges_sha256, peaks  # type: ignore
