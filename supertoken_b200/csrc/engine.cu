@@ -62,6 +62,7 @@ struct stbpe_engine {
     uint32_t *graph_tiles;
     cudaStream_t graph_stream;
     bool use_graph;
+    int part_group;       // partitions per launch of the second pass of the partitioned count
     bool use_pdl;         // the captured single-GPU loop launches its kernels as programmatic dependents
     bool pdl_now;         // set while that loop is being captured
     std::string err;
@@ -222,6 +223,8 @@ STBPE_VISIBLE int stbpe_create(stbpe_engine **out, const stbpe_config *cfg) {
     memset(e->mail_mapped, 0, sizeof(e->mail_mapped));
     e->peers_open = false;
     e->use_graph = getenv("STBPE_NO_GRAPH") == nullptr;
+    e->part_group = STBPE_PARTS;
+    if (const char *v = getenv("STBPE_PART_GROUP")) e->part_group = atoi(v) > 0 ? atoi(v) : STBPE_PARTS;
     e->use_pdl = getenv("STBPE_NO_PDL") == nullptr;
     e->pdl_now = false;
     e->filter_valid = false;
@@ -652,8 +655,13 @@ static int launch_count(stbpe_engine *e, bool mg, cudaStream_t s) {
             dense_to_table_kernel<false><<<256, 256, 0, s>>>(e->d, e->wide_dense);
             CK(cudaGetLastError());
             const int per_region = 2;  // blocks per pass-1 region: a region holds some 10^4 words
-            for (int p = 0; p < STBPE_PARTS; ++p)
-                partition_table_kernel<<<pb.n_cta * per_region, 1024, 0, s>>>(e->d, pb, p, per_region);
+            // all partitions in a few launches: the blocks of a launch are scheduled in partition
+            // order, so two or three table slices are being filled at any time and stay in L2, and
+            // the tail of a partition runs under the start of the next
+            for (int p = 0; p < STBPE_PARTS; p += e->part_group) {
+                const int n = STBPE_PARTS - p < e->part_group ? STBPE_PARTS - p : e->part_group;
+                partition_table_kernel<<<pb.n_cta * per_region * n, 1024, 0, s>>>(e->d, pb, p, per_region);
+            }
             CK(cudaGetLastError());
             CK(cudaEventRecord(e->ev1, s));
             CK(cudaEventSynchronize(e->ev1));
@@ -1308,8 +1316,11 @@ STBPE_VISIBLE int stbpe_mg_wide_pass2(stbpe_engine *e, void *stream) {
     CK(cudaEventRecord(e->ev0, s));
     dense_peers_to_table_kernel<<<256, 256, 0, s>>>(e->d, e->wide_peers, n_cta);
     CK(cudaGetLastError());
-    for (int p = e->cfg.rank; p < STBPE_PARTS; p += world)
-        partition_table_peers_kernel<<<n_cta * 2, 1024, 0, s>>>(e->d, e->wide_peers, p, n_cta);
+    const int owned = (STBPE_PARTS - e->cfg.rank + world - 1) / world;  // partitions rank, rank + world, ...
+    for (int i = 0; i < owned; i += e->part_group) {
+        const int n = owned - i < e->part_group ? owned - i : e->part_group;
+        partition_table_peers_kernel<<<n_cta * 2 * n, 1024, 0, s>>>(e->d, e->wide_peers, e->cfg.rank + i * world, world, n_cta);
+    }
     CK(cudaGetLastError());
     CK(cudaEventRecord(e->ev1, s));
     CK(cudaEventSynchronize(e->ev1));

@@ -226,7 +226,12 @@ __device__ __forceinline__ void part_word_to_table(const EngineDev &e, uint32_t 
 // alone took longer than everything else of its launch), so every block first collects its words in
 // a direct-mapped cache in shared memory (word -> count; a word whose entry is taken by another
 // goes straight to the table) and then adds each cached word once.
-__global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, PartBuffers pb, int p, int per_region) {
+// One launch serves several partitions: consecutive groups of n_cta * per_region blocks take
+// consecutive partitions, so the blocks resident at any time work on two or three slices.
+__global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, PartBuffers pb, int p_first, int per_region) {
+    const int blocks_per_part = pb.n_cta * per_region;
+    const int p = p_first + (int)(blockIdx.x / blocks_per_part);
+    const int block = (int)(blockIdx.x % blocks_per_part);
     __shared__ uint32_t s_word[STBPE_PART_CACHE];
     __shared__ unsigned int s_cnt[STBPE_PART_CACHE];
     for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
@@ -234,7 +239,7 @@ __global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, Part
         s_cnt[i] = 0u;
     }
     __syncthreads();
-    const int region = blockIdx.x / per_region, part = blockIdx.x % per_region;
+    const int region = block / per_region, part = block % per_region;
     const u64 top = (u64)slice_of(e, (unsigned int)p) << e.slot_bits;
     const i64 n = pb.fill[(i64)p * pb.n_cta + region];
     const uint32_t *w = pb.words + ((i64)p * pb.n_cta + region) * pb.cap;
@@ -268,7 +273,11 @@ __global__ void __launch_bounds__(1024) partition_table_kernel(EngineDev e, Part
 // is one wave of blocks whatever the number of ranks; a block walks over its share of the
 // (source rank, region, half) units with one cache, which it adds to the table at the end.
 __global__ void __launch_bounds__(1024)
-    partition_table_peers_kernel(EngineDev e, WidePeers wp, int p, int n_cta) {
+    partition_table_peers_kernel(EngineDev e, WidePeers wp, int p_first, int p_step, int n_cta) {
+    // consecutive groups of 2 * n_cta blocks take the partitions p_first, p_first + p_step, ...
+    const int blocks_per_part = 2 * n_cta;
+    const int p = p_first + (int)(blockIdx.x / blocks_per_part) * p_step;
+    const int block = (int)(blockIdx.x % blocks_per_part);
     __shared__ uint32_t s_word[STBPE_PART_CACHE];
     __shared__ unsigned int s_cnt[STBPE_PART_CACHE];
     for (int i = threadIdx.x; i < STBPE_PART_CACHE; i += blockDim.x) {
@@ -279,7 +288,7 @@ __global__ void __launch_bounds__(1024)
     unsigned int fresh = 0;
     const u64 top = (u64)slice_of(e, (unsigned int)p) << e.slot_bits;
     const int n_units = wp.world * n_cta * 2;
-    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+    for (int unit = block; unit < n_units; unit += blocks_per_part) {
         const int half = unit & 1, region = (unit >> 1) % n_cta, src = (unit >> 1) / n_cta;
         const unsigned char *blk = wp.block[src];
         const WideHeader hd = *reinterpret_cast<const WideHeader *>(blk);

@@ -107,6 +107,20 @@ def test_fit_bytes_and_artifacts(tmp_path):
     assert t3.fit_bytes(c.data, c.row_offsets)["merges"] == om
 
 
+def test_fit_bytes_from_pinned_pageable_and_device_memory():
+    """The same bytes from pinned host memory, pageable host memory and device memory give the
+    oracle's merges (a host buffer is copied in pieces under the pack kernel)."""
+    c = synth.config2_mixed(1 << 20, seed=5, lexicon=1200, mean_doc_bytes=900)
+    ids, off = O.flatten_rows(corpus_rows(c))
+    om, _, _ = O.train_flat(ids, off, 256, 48, 1)
+    host = torch.from_numpy(np.ascontiguousarray(c.data))
+    pinned = torch.empty(host.numel(), dtype=torch.uint8, pin_memory=True)
+    pinned.copy_(host)
+    for data in (pinned, host, host.cuda()):
+        t = GPUBPETrainer(merges=48, device="cuda:0")
+        assert t.fit_bytes(data, c.row_offsets, log_every=0)["merges"] == om
+
+
 def test_resume_equals_uninterrupted_run_and_warm_start_plan(tmp_path):
     c = synth.config2_mixed(1 << 18, seed=21, lexicon=1500, mean_doc_bytes=600)
     rows = [r.tolist() for r in corpus_rows(c)]
