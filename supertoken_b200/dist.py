@@ -715,4 +715,5 @@ def run_count_bench_multi(args, wl, rank: int, local_rank: int, world: int) -> N
                          "frac": gbs / (peak * world), "kernels_only_ms": kernel_ms, "traffic": None},
             "e2e": {"value": 4.0 * n_tokens / e2e_s / 1e9, "unit": "GB/s", "seconds": e2e_s,
                     "h2d_bytes_per_step": 4.0 * n_tokens, "d2h_bytes_per_step": 24.0},
-            "gpu_launches": (2 + 256 // world + 6) * K, "clocks": None, "cpu_baseline": None}), flush=True)
+            "gpu_launches": (3 + 6) * K,   # first pass, hot pairs, second pass; the six launches of the count round
+             "clocks": None, "cpu_baseline": None}), flush=True)
