@@ -498,7 +498,7 @@ def main():
                              f"{scale:.4f} to the full corpus (recount cost is linear in tokens)"}
         del ids, off
 
-    # the initial pair count BASELINE.json names as its microbenchmark (config 3: 2^31 ids over a
+    # the initial pair count that is the path's microbenchmark (config 3: 2^31 ids over a
     # 65 536 vocabulary), two passes beside the merge job so that it reaches the same record
     pair_count_c3 = None
     if args.workload == "c2" and not args.bytes and not args.no_c3:

@@ -1,5 +1,6 @@
 """Host-side logic that needs no GPU: generators, artifact formats, batch flattening."""
 import json
+import os
 
 import numpy as np
 import pytest
@@ -149,10 +150,12 @@ def test_checkpoints_written_by_the_reference_load(tmp_path):
     assert state["payload"]["trainer"]["model"]["merges"] == tie["checkpoint_after_6"]["trainer"]["model"]["merges"]
 
 
-REFERENCE = "/root/reference"
+# the reference checkout, when there is one beside the build (STBPE_REFERENCE_DIR names another place)
+_HERE = os.path.dirname(os.path.abspath(__file__))
+REFERENCE = os.environ.get("STBPE_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 
 
-@pytest.mark.skipif(not __import__("os").path.isdir(REFERENCE), reason="needs the reference checkout")
+@pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="needs the reference checkout")
 def test_drop_in_seam_of_the_reference_command_line(tmp_path, monkeypatch):
     """The swap a maintainer makes: rebind ``GPUBPETrainer`` in the reference's modules, then use the
     reference's own ``train-bpe`` parser and trainer factory (``main.py:21-30``, ``:661-689``, ``:2180-2363``).
