@@ -203,3 +203,46 @@ def test_drop_in_seam_of_the_reference_command_line(tmp_path, monkeypatch):
             sys.modules.pop(m, None)
         importlib.reload(base_mod)
         importlib.reload(ours_mod)
+
+
+def test_warm_start_sources_in_every_accepted_form(tmp_path):
+    """``train-bpe --warm-start`` takes a JSON manifest (merges at the top level, under ``trainer`` or
+    under ``trainer.model``), a bare JSON list, a ``.tiktoken`` rank table or a directory holding one
+    of the exported files (``main.py:501-575`` of the reference); anything else ends the command."""
+    merges = [(104, 101), (108, 108), (256, 257), (258, 111)]          # h e | l l | he ll | hell o
+    as_lists = [list(p) for p in merges]
+    forms = {"top.json": {"merges": as_lists}, "trainer.json": {"trainer": {"merges": as_lists}},
+             "model.json": {"trainer": {"model": {"merges": as_lists}}}, "bare.json": as_lists}
+    for name, payload in forms.items():
+        (tmp_path / name).write_text(json.dumps(payload))
+        assert load_warm_start_merges(str(tmp_path / name)) == merges, name
+    paths = write_artifacts(str(tmp_path / "out"), 256, merges, 260)
+    assert load_warm_start_merges(paths["tiktoken_merges"]) == merges
+    assert load_warm_start_merges(str(tmp_path / "out")) == merges          # directory: merges.tiktoken first
+    os.remove(paths["tiktoken_merges"])
+    assert load_warm_start_merges(str(tmp_path / "out")) == merges          # then bpe_merges.json
+    assert load_warm_start_merges(None) is None and load_warm_start_merges("") is None
+    (tmp_path / "empty").mkdir()
+    (tmp_path / "bad.json").write_text(json.dumps({"merges": [[1, 2, 3]]}))
+    (tmp_path / "none.json").write_text(json.dumps({"trainer": {}}))
+    (tmp_path / "plan.txt").write_text("1 2\n")
+    for bad in ("missing.json", "empty", "bad.json", "none.json", "plan.txt"):
+        with pytest.raises(SystemExit):
+            load_warm_start_merges(str(tmp_path / bad))
+
+
+def test_round_budget_between_host_checks_is_the_same_on_every_rank():
+    """Ranks enqueue rounds without talking to each other, so the number of rounds until the next look
+    at the device state may depend only on what all ranks know: merges committed and the target."""
+    from supertoken_b200.dist import rounds_until_next_check
+    assert rounds_until_next_check(0, 32000, 256) == 32            # early: re-pack and filter decisions
+    assert rounds_until_next_check(511, 32000, 256) == 32
+    assert rounds_until_next_check(512, 32000, 256) == 256
+    assert rounds_until_next_check(0, 20, 256) == 21               # never more than the target needs (+1 applies the last)
+    assert rounds_until_next_check(19, 20, 256) == 2
+    assert rounds_until_next_check(20, 20, 256) == 1               # always progress
+    assert rounds_until_next_check(100, 20, 8) == 1
+    for done in range(0, 700, 37):
+        for target in (1, 50, 600, 32000):
+            n = rounds_until_next_check(done, target, 256)
+            assert 1 <= n <= 256 and (done >= target or n <= target - done + 1)
